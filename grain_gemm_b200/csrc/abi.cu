@@ -1,0 +1,565 @@
+// extern "C" entry points of libgrain_b200.so (declared in include/grain_gemm_b200.h):
+// argument checks, tensor-map encoding, variant selection and kernel launches.
+// Nothing here allocates or synchronises (gg_device_status excepted, which reads back a word).
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/grain_gemm_b200.h"
+#include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
+#include "moe_gate_up_tc.cuh"
+#include "moe_route.cuh"
+
+namespace gg {
+
+constexpr int kAbiVersion = 1;
+
+// ---------------------------------------------------------------- host helpers
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) !=
+            cudaSuccess ||
+        query != cudaDriverEntryPointSuccess) {
+      ptr = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// Tensor map over a row-major int8 matrix [rows, cols] with row pitch `pitch` bytes; boxes of
+// 128 bytes x box_rows with the 128-byte swizzle; out-of-range elements read as zero.
+static int encode_int8_rows(CUtensorMap* map, const void* base, long long rows, long long cols,
+                            long long pitch, int box_rows) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return static_cast<int>(cudaErrorNotSupported);
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch)};
+  const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t element_strides[2] = {1u, 1u};
+  const CUresult result = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base),
+                                 dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return result == CUDA_SUCCESS ? 0 : -10000 - static_cast<int>(result);
+}
+
+static int sm_count() {
+  // Immutable device property, cached per device.
+  static int cached[64] = {0};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+  if (cached[device] == 0) {
+    int count = 0;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        count <= 0) {
+      count = 148;
+    }
+    cached[device] = count;
+  }
+  return cached[device];
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct GemmArgs {
+  const void *a, *b, *scale_a, *scale_b;
+  void* c;
+  int m, n, k;
+  long long a_sm, a_sk, b_sk, b_sn, sa_sm, sa_sg, sb_sg, sb_sn, ldc;
+  int group_size, out_dtype;
+};
+
+static bool valid_group(int g) { return g == 32 || g == 64 || g == 128 || g == 256; }
+
+static bool tensor_core_layout(const GemmArgs& g) {
+  return g.a_sk == 1 && g.b_sk == 1 && g.a_sm % 16 == 0 && g.b_sn % 16 == 0 && g.a_sm >= g.k &&
+         g.b_sn >= g.k && aligned16(g.a) && aligned16(g.b);
+}
+
+static int select_variant(const GemmArgs& g) {
+  if (!tensor_core_layout(g)) return GG_VARIANT_SIMT;
+  const int sms = sm_count();
+  const long long tiles_256 = static_cast<long long>((g.m + 127) / 128) * ((g.n + 255) / 256);
+  if (g.m > 128 && tiles_256 >= sms) return GG_VARIANT_TC_PAIR_N256;
+  if (tiles_256 >= sms) return GG_VARIANT_TC_N256;
+  const long long tiles_128 = static_cast<long long>((g.m + 127) / 128) * ((g.n + 127) / 128);
+  if (tiles_128 >= sms) return GG_VARIANT_TC_N128;
+  return GG_VARIANT_TC_N64;
+}
+
+template <typename OutT, bool kRagged>
+static int launch_simt(const GemmSimtParams& p, int row_tiles, cudaStream_t stream) {
+  const dim3 grid((p.n + kSimtTile - 1) / kSimtTile, row_tiles);
+  if (grid.x == 0 || grid.y == 0) return 0;
+  if (grid.y > 65535) return static_cast<int>(cudaErrorInvalidValue);
+  gemm_simt_kernel<OutT, kRagged><<<grid, 256, 0, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <bool kRagged>
+static int launch_simt_dtype(const GemmSimtParams& p, int row_tiles, int out_dtype,
+                             cudaStream_t stream) {
+  switch (out_dtype) {
+    case GG_OUT_FP32: return launch_simt<float, kRagged>(p, row_tiles, stream);
+    case GG_OUT_BF16: return launch_simt<__nv_bfloat16, kRagged>(p, row_tiles, stream);
+    case GG_OUT_FP16: return launch_simt<__half, kRagged>(p, row_tiles, stream);
+    default: return static_cast<int>(cudaErrorInvalidValue);
+  }
+}
+
+static GemmSimtParams simt_params(const GemmArgs& g) {
+  GemmSimtParams p = {};
+  p.a = static_cast<const int8_t*>(g.a);
+  p.b = static_cast<const int8_t*>(g.b);
+  p.scale_a = static_cast<const float*>(g.scale_a);
+  p.scale_b = static_cast<const float*>(g.scale_b);
+  p.c = g.c;
+  p.m = g.m; p.n = g.n; p.k = g.k;
+  p.a_sm = g.a_sm; p.a_sk = g.a_sk; p.b_sk = g.b_sk; p.b_sn = g.b_sn;
+  p.sa_sm = g.sa_sm; p.sa_sg = g.sa_sg; p.sb_sg = g.sb_sg; p.sb_sn = g.sb_sn;
+  p.ldc = g.ldc;
+  p.group_size = g.group_size;
+  return p;
+}
+
+template <int kCtaGroup, int BN, int kStages, typename OutT, bool kGrouped>
+static int launch_tc_kernel(const CUtensorMap& map_a, const CUtensorMap& map_b,
+                            const GemmTcParams& p, cudaStream_t stream) {
+  using Shape = GemmTcShape<kCtaGroup, BN, kStages>;
+  auto kernel = gemm_tc_kernel<kCtaGroup, BN, kStages, OutT, kGrouped>;
+  cudaError_t error =
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape::kSmemBytes);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const int workers = static_cast<int>(tiles < sm_count() / kCtaGroup ? tiles : sm_count() / kCtaGroup);
+  if (workers <= 0) return 0;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(workers * kCtaGroup);
+  config.blockDim = dim3(Shape::kThreads);
+  config.dynamicSmemBytes = Shape::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = kCtaGroup;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  error = cudaLaunchKernelEx(&config, kernel, map_a, map_b, p);
+  return static_cast<int>(error);
+}
+
+template <int kCtaGroup, int BN, int kStages, bool kGrouped>
+static int launch_tc_dtype(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmTcParams& p,
+                           int out_dtype, cudaStream_t stream) {
+  switch (out_dtype) {
+    case GG_OUT_FP32:
+      if constexpr (kGrouped) return static_cast<int>(cudaErrorInvalidValue);
+      else return launch_tc_kernel<kCtaGroup, BN, kStages, float, kGrouped>(map_a, map_b, p, stream);
+    case GG_OUT_BF16:
+      return launch_tc_kernel<kCtaGroup, BN, kStages, __nv_bfloat16, kGrouped>(map_a, map_b, p, stream);
+    case GG_OUT_FP16:
+      return launch_tc_kernel<kCtaGroup, BN, kStages, __half, kGrouped>(map_a, map_b, p, stream);
+    default: return static_cast<int>(cudaErrorInvalidValue);
+  }
+}
+
+static int launch_gemm_tc(const GemmArgs& g, int variant, cudaStream_t stream) {
+  const bool pair = variant == GG_VARIANT_TC_PAIR_N256 || variant == GG_VARIANT_TC_PAIR_N128;
+  const int bn = (variant == GG_VARIANT_TC_N256 || variant == GG_VARIANT_TC_PAIR_N256) ? 256
+                 : (variant == GG_VARIANT_TC_N128 || variant == GG_VARIANT_TC_PAIR_N128) ? 128
+                                                                                         : 64;
+  CUtensorMap map_a, map_b;
+  int status = encode_int8_rows(&map_a, g.a, g.m, g.k, g.a_sm, 128);
+  if (status) return status;
+  status = encode_int8_rows(&map_b, g.b, g.n, g.k, g.b_sn, pair ? bn / 2 : bn);
+  if (status) return status;
+  GemmTcParams p = {};
+  p.scale_a = static_cast<const float*>(g.scale_a);
+  p.scale_b = static_cast<const float*>(g.scale_b);
+  p.c = g.c;
+  p.m = g.m; p.n = g.n; p.k = g.k;
+  p.sa_sm = g.sa_sm; p.sa_sg = g.sa_sg; p.sb_sg = g.sb_sg; p.sb_sn = g.sb_sn;
+  p.ldc = g.ldc;
+  p.group_size = g.group_size;
+  p.tiles_m = (g.m + (pair ? 255 : 127)) / (pair ? 256 : 128);
+  p.tiles_n = (g.n + bn - 1) / bn;
+  const int out_bytes = g.out_dtype == GG_OUT_FP32 ? 4 : 2;
+  p.c_vector_ok = aligned16(g.c) && (g.ldc * out_bytes) % 16 == 0;
+  switch (variant) {
+    case GG_VARIANT_TC_N256: return launch_tc_dtype<1, 256, 4, false>(map_a, map_b, p, g.out_dtype, stream);
+    case GG_VARIANT_TC_N128: return launch_tc_dtype<1, 128, 6, false>(map_a, map_b, p, g.out_dtype, stream);
+    case GG_VARIANT_TC_N64: return launch_tc_dtype<1, 64, 8, false>(map_a, map_b, p, g.out_dtype, stream);
+    case GG_VARIANT_TC_PAIR_N256: return launch_tc_dtype<2, 256, 6, false>(map_a, map_b, p, g.out_dtype, stream);
+    case GG_VARIANT_TC_PAIR_N128: return launch_tc_dtype<2, 128, 8, false>(map_a, map_b, p, g.out_dtype, stream);
+    default: return static_cast<int>(cudaErrorInvalidValue);
+  }
+}
+
+static int run_gemm(const GemmArgs& g, int variant, cudaStream_t stream) {
+  if (g.m < 0 || g.n < 0 || g.k < 0 || !valid_group(g.group_size) || g.out_dtype < 0 ||
+      g.out_dtype > 2 || g.a_sm <= 0 || g.a_sk <= 0 || g.b_sk <= 0 || g.b_sn <= 0 || g.ldc < g.n) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (g.m == 0 || g.n == 0) return 0;
+  if (g.k == 0) return static_cast<int>(cudaErrorInvalidValue);  // callers zero-fill instead
+  if (!g.a || !g.b || !g.scale_a || !g.scale_b || !g.c) return static_cast<int>(cudaErrorInvalidValue);
+  if (variant == GG_VARIANT_AUTO) variant = select_variant(g);
+  if (variant == GG_VARIANT_SIMT) {
+    return launch_simt_dtype<false>(simt_params(g), (g.m + kSimtTile - 1) / kSimtTile, g.out_dtype,
+                                    stream);
+  }
+  if (variant < GG_VARIANT_TC_N256 || variant > GG_VARIANT_TC_PAIR_N128 || !tensor_core_layout(g)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  return launch_gemm_tc(g, variant, stream);
+}
+
+}  // namespace gg
+
+// ------------------------------------------------------------------ extern "C"
+
+extern "C" {
+
+int gg_abi_version(void) { return gg::kAbiVersion; }
+
+const char* gg_error_string(int status) {
+  if (status == 0) return "success";
+  if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  if (status <= -10000) {
+    static thread_local char text[64];
+    snprintf(text, sizeof(text), "tensor map encoding failed (CUresult %d)", -10000 - status);
+    return text;
+  }
+  return "unknown status";
+}
+
+const char* grain_cuda_error_string(int status) { return gg_error_string(status); }
+
+int gg_int8_gemm(const void* a, const void* b, const void* scale_a, const void* scale_b, void* c,
+                 int m, int n, int k, long long a_sm, long long a_sk, long long b_sk,
+                 long long b_sn, long long sa_sm, long long sa_sg, long long sb_sg, long long sb_sn,
+                 long long ldc, int group_size, int out_dtype, int variant, void* stream) {
+  const gg::GemmArgs g = {a, b, scale_a, scale_b, c, m, n, k, a_sm, a_sk, b_sk, b_sn,
+                          sa_sm, sa_sg, sb_sg, sb_sn, ldc, group_size, out_dtype};
+  return gg::run_gemm(g, variant, static_cast<cudaStream_t>(stream));
+}
+
+int gg_int8_gemm_select(const void* a, const void* b, const void* c, int m, int n, int k,
+                        long long a_sm, long long a_sk, long long b_sk, long long b_sn,
+                        long long ldc, int group_size, int out_dtype) {
+  const gg::GemmArgs g = {a, b, nullptr, nullptr, const_cast<void*>(c), m, n, k, a_sm, a_sk, b_sk,
+                          b_sn, 0, 0, 0, 0, ldc, group_size, out_dtype};
+  return gg::select_variant(g);
+}
+
+int gg_int8_gemm_partials(const void* a, const void* b, const void* scale_a, const void* scale_b,
+                          void* c_fp32, void* partials, int m, int n, int k, long long a_sm,
+                          long long a_sk, long long b_sk, long long b_sn, long long sa_sm,
+                          long long sa_sg, long long sb_sg, long long sb_sn, int group_size,
+                          void* stream) {
+  if (m <= 0 || n <= 0 || k <= 0 || !gg::valid_group(group_size) || !partials || !c_fp32) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  const gg::GemmArgs g = {a, b, scale_a, scale_b, c_fp32, m, n, k, a_sm, a_sk, b_sk, b_sn,
+                          sa_sm, sa_sg, sb_sg, sb_sn, n, group_size, GG_OUT_FP32};
+  gg::GemmSimtParams p = gg::simt_params(g);
+  p.partials = static_cast<int*>(partials);
+  return gg::launch_simt_dtype<false>(p, (m + gg::kSimtTile - 1) / gg::kSimtTile, GG_OUT_FP32,
+                                      static_cast<cudaStream_t>(stream));
+}
+
+int grain_cute_g256(const void* a, const void* b, const void* scale_a, const void* scale_b,
+                    void* c, int m, int n, int k, int config, void* stream) {
+  (void)config;
+  if (m <= 0 || n <= 0 || k <= 0 || k % 256) return static_cast<int>(cudaErrorInvalidValue);
+  const int groups = k / 256;
+  const gg::GemmArgs g = {a, b, scale_a, scale_b, c, m, n, k, k, 1, 1, k,
+                          groups, 1, n, 1, n, 256, GG_OUT_BF16};
+  return gg::run_gemm(g, GG_VARIANT_AUTO, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------- MoE
+
+size_t gg_moe_route_workspace_bytes(int tokens, int top_k, int experts) {
+  const long long slots = static_cast<long long>(tokens) * top_k;
+  if (slots <= gg::kRouteChunk) return 0;
+  const long long chunks = (slots + gg::kRouteChunk - 1) / gg::kRouteChunk;
+  return static_cast<size_t>(chunks * (experts + 2)) * sizeof(int);
+}
+
+int gg_moe_route(const void* ids, int ids_are_i64, const void* mask, int tokens, int top_k,
+                 int experts, void* effective_ids, void* order, void* inverse, void* counts,
+                 void* offsets, void* statistics, void* workspace, size_t workspace_bytes,
+                 void* stream_ptr) {
+  if (tokens < 0 || top_k <= 0 || experts <= 0 || !counts || !offsets || !statistics) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  gg::RouteParams p = {};
+  p.ids = ids;
+  p.ids_are_i64 = ids_are_i64;
+  p.mask = static_cast<const uint8_t*>(mask);
+  p.tokens = tokens; p.top_k = top_k; p.experts = experts;
+  p.effective_ids = effective_ids;
+  p.order = static_cast<long long*>(order);
+  p.inverse = static_cast<int*>(inverse);
+  p.counts = static_cast<int*>(counts);
+  p.offsets = static_cast<int*>(offsets);
+  p.statistics = static_cast<int*>(statistics);
+  p.workspace = static_cast<int*>(workspace);
+  const long long slots = static_cast<long long>(tokens) * top_k;
+  const size_t smem = static_cast<size_t>(experts + 2) * sizeof(int);
+  if (smem > 200 * 1024) return static_cast<int>(cudaErrorInvalidValue);
+  cudaError_t error;
+  if (slots <= gg::kRouteChunk) {
+    if (smem > 48 * 1024) {
+      error = cudaFuncSetAttribute(gg::route_single_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (error != cudaSuccess) return static_cast<int>(error);
+    }
+    gg::route_single_kernel<<<1, gg::kRouteChunk, smem, stream>>>(p);
+    return static_cast<int>(cudaGetLastError());
+  }
+  if (!ids || !effective_ids || !order || !inverse) return static_cast<int>(cudaErrorInvalidValue);
+  if (workspace_bytes < gg_moe_route_workspace_bytes(tokens, top_k, experts) || !workspace) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  const int chunks = static_cast<int>((slots + gg::kRouteChunk - 1) / gg::kRouteChunk);
+  if (smem > 48 * 1024) {
+    for (const void* kernel : {reinterpret_cast<const void*>(gg::route_histogram_kernel),
+                               reinterpret_cast<const void*>(gg::route_scan_kernel),
+                               reinterpret_cast<const void*>(gg::route_place_kernel)}) {
+      error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(smem));
+      if (error != cudaSuccess) return static_cast<int>(error);
+    }
+  }
+  gg::route_histogram_kernel<<<chunks, gg::kRouteChunk, smem, stream>>>(p);
+  gg::route_scan_kernel<<<1, 1024, smem, stream>>>(p, chunks);
+  gg::route_place_kernel<<<chunks, gg::kRouteChunk, smem, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gg_moe_tile_capacity(int assignments, int experts, int tile_rows) {
+  if (assignments < 0 || experts <= 0 || tile_rows <= 0) return 0;
+  return (assignments + tile_rows - 1) / tile_rows + experts;
+}
+
+int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, void* tile_expert,
+                 void* tile_row, void* stream) {
+  if (!offsets || !tile_expert || !tile_row || experts <= 0 || tile_rows <= 0 || capacity <= 0) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  const size_t smem = static_cast<size_t>(experts + 1) * sizeof(int);
+  if (smem > 48 * 1024) return static_cast<int>(cudaErrorInvalidValue);
+  gg::moe_tiles_kernel<<<1, 1024, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const int*>(offsets), experts, tile_rows, capacity, static_cast<int*>(tile_expert),
+      static_cast<int*>(tile_row));
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const void* scale_w1,
+                   const void* order, const void* offsets, const void* tile_expert,
+                   const void* tile_row, int tile_capacity, int tile_rows, void* q, void* s,
+                   void* gate_up_scratch, int tokens, int top_k, int experts, int hidden,
+                   int intermediate, int interleaved, int out_dtype, void* stream_ptr) {
+  if (tokens <= 0 || top_k <= 0 || experts <= 0 || hidden <= 0 || intermediate <= 0 ||
+      hidden % 256 || intermediate % 256 || tile_capacity <= 0 ||
+      (out_dtype != GG_OUT_BF16 && out_dtype != GG_OUT_FP16) || !x || !scale_x || !w1 ||
+      !scale_w1 || !order || !offsets || !tile_expert || !tile_row || !q || !s) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const long long slots = static_cast<long long>(tokens) * top_k;
+  if (tile_rows == 128) {
+    if (!gg::aligned16(x) || !gg::aligned16(w1) || !gg::aligned16(q)) {
+      return static_cast<int>(cudaErrorInvalidValue);
+    }
+    CUtensorMap map_w;
+    const int status = gg::encode_int8_rows(&map_w, w1, static_cast<long long>(experts) * 2 * intermediate,
+                                            hidden, hidden, 128);
+    if (status) return status;
+    gg::GateUpParams p = {};
+    p.x = static_cast<const int8_t*>(x);
+    p.scale_x = static_cast<const float*>(scale_x);
+    p.scale_w = static_cast<const float*>(scale_w1);
+    p.order = static_cast<const long long*>(order);
+    p.expert_offsets = static_cast<const int*>(offsets);
+    p.tile_expert = static_cast<const int*>(tile_expert);
+    p.tile_row = static_cast<const int*>(tile_row);
+    p.q = static_cast<int8_t*>(q);
+    p.s = static_cast<float*>(s);
+    p.top_k = top_k; p.hidden = hidden; p.intermediate = intermediate;
+    p.max_tiles = tile_capacity; p.interleaved = interleaved;
+    const long long items = static_cast<long long>(tile_capacity) * (intermediate / 256);
+    const int grid = static_cast<int>(items < gg::sm_count() ? items : gg::sm_count());
+    cudaError_t error;
+    if (out_dtype == GG_OUT_BF16) {
+      auto kernel = gg::moe_gate_up_tc_kernel<__nv_bfloat16>;
+      error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   gg::GateUpShape::kSmemBytes);
+      if (error != cudaSuccess) return static_cast<int>(error);
+      kernel<<<grid, 384, gg::GateUpShape::kSmemBytes, stream>>>(map_w, p);
+    } else {
+      auto kernel = gg::moe_gate_up_tc_kernel<__half>;
+      error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   gg::GateUpShape::kSmemBytes);
+      if (error != cudaSuccess) return static_cast<int>(error);
+      kernel<<<grid, 384, gg::GateUpShape::kSmemBytes, stream>>>(map_w, p);
+    }
+    return static_cast<int>(cudaGetLastError());
+  }
+  if (tile_rows != gg::kSimtTile || !gate_up_scratch) return static_cast<int>(cudaErrorInvalidValue);
+  // CUDA-core path: ragged gathered GEMM into the scratch matrix, then SwiGLU + requantisation.
+  gg::GemmSimtParams p = {};
+  p.a = static_cast<const int8_t*>(x);
+  p.b = static_cast<const int8_t*>(w1);
+  p.scale_a = static_cast<const float*>(scale_x);
+  p.scale_b = static_cast<const float*>(scale_w1);
+  p.c = gate_up_scratch;
+  p.m = static_cast<int>(slots); p.n = 2 * intermediate; p.k = hidden;
+  p.a_sm = hidden; p.a_sk = 1; p.b_sk = 1; p.b_sn = hidden;
+  p.sa_sm = hidden / 256; p.sa_sg = 1; p.sb_sg = 2 * intermediate; p.sb_sn = 1;
+  p.ldc = 2 * intermediate;
+  p.group_size = 256;
+  p.order = static_cast<const long long*>(order);
+  p.top_k = top_k;
+  p.expert_offsets = static_cast<const int*>(offsets);
+  p.tile_expert = static_cast<const int*>(tile_expert);
+  p.tile_row = static_cast<const int*>(tile_row);
+  p.b_expert_stride = static_cast<long long>(2) * intermediate * hidden;
+  p.sb_expert_stride = static_cast<long long>(hidden / 256) * 2 * intermediate;
+  int status = gg::launch_simt_dtype<true>(p, tile_capacity, out_dtype, stream);
+  if (status) return status;
+  const long long items = slots * (intermediate / 256);
+  const unsigned blocks = static_cast<unsigned>((items + 7) / 8);
+  const int* valid = static_cast<const int*>(offsets) + experts;
+  if (out_dtype == GG_OUT_BF16) {
+    gg::swiglu_quantize_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(gate_up_scratch), slots, valid, intermediate, interleaved,
+        static_cast<int8_t*>(q), static_cast<float*>(s));
+  } else {
+    gg::swiglu_quantize_kernel<__half><<<blocks, 256, 0, stream>>>(
+        static_cast<const __half*>(gate_up_scratch), slots, valid, intermediate, interleaved,
+        static_cast<int8_t*>(q), static_cast<float*>(s));
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_w2,
+                const void* offsets, const void* tile_expert, const void* tile_row,
+                int tile_capacity, int tile_rows, void* expert_out, int assignments, int experts,
+                int hidden, int intermediate, int out_dtype, void* stream_ptr) {
+  if (assignments <= 0 || experts <= 0 || hidden <= 0 || intermediate <= 0 || intermediate % 256 ||
+      tile_capacity <= 0 || (out_dtype != GG_OUT_BF16 && out_dtype != GG_OUT_FP16) || !q || !s ||
+      !w2 || !scale_w2 || !offsets || !tile_expert || !tile_row || !expert_out) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (tile_rows == 128) {
+    if (!gg::aligned16(q) || !gg::aligned16(w2) || !gg::aligned16(expert_out) || hidden % 8) {
+      return static_cast<int>(cudaErrorInvalidValue);
+    }
+    CUtensorMap map_a, map_b;
+    int status = gg::encode_int8_rows(&map_a, q, assignments, intermediate, intermediate, 128);
+    if (status) return status;
+    const int bn = hidden >= 256 ? 256 : hidden >= 128 ? 128 : 64;
+    status = gg::encode_int8_rows(&map_b, w2, static_cast<long long>(experts) * hidden, intermediate,
+                                  intermediate, bn);
+    if (status) return status;
+    gg::GemmTcParams p = {};
+    p.scale_a = static_cast<const float*>(s);
+    p.scale_b = static_cast<const float*>(scale_w2);
+    p.c = expert_out;
+    p.m = assignments; p.n = hidden; p.k = intermediate;
+    p.sa_sm = intermediate / 256; p.sa_sg = 1; p.sb_sg = hidden; p.sb_sn = 1;
+    p.ldc = hidden;
+    p.group_size = 256;
+    p.tiles_m = tile_capacity;
+    p.tiles_n = (hidden + bn - 1) / bn;
+    p.c_vector_ok = 1;
+    p.expert_offsets = static_cast<const int*>(offsets);
+    p.tile_expert = static_cast<const int*>(tile_expert);
+    p.tile_row = static_cast<const int*>(tile_row);
+    p.b_rows_per_expert = hidden;
+    p.sb_expert_stride = static_cast<long long>(intermediate / 256) * hidden;
+    if (bn == 256) return gg::launch_tc_dtype<1, 256, 4, true>(map_a, map_b, p, out_dtype, stream);
+    if (bn == 128) return gg::launch_tc_dtype<1, 128, 6, true>(map_a, map_b, p, out_dtype, stream);
+    return gg::launch_tc_dtype<1, 64, 8, true>(map_a, map_b, p, out_dtype, stream);
+  }
+  if (tile_rows != gg::kSimtTile) return static_cast<int>(cudaErrorInvalidValue);
+  gg::GemmSimtParams p = {};
+  p.a = static_cast<const int8_t*>(q);
+  p.b = static_cast<const int8_t*>(w2);
+  p.scale_a = static_cast<const float*>(s);
+  p.scale_b = static_cast<const float*>(scale_w2);
+  p.c = expert_out;
+  p.m = assignments; p.n = hidden; p.k = intermediate;
+  p.a_sm = intermediate; p.a_sk = 1; p.b_sk = 1; p.b_sn = intermediate;
+  p.sa_sm = intermediate / 256; p.sa_sg = 1; p.sb_sg = hidden; p.sb_sn = 1;
+  p.ldc = hidden;
+  p.group_size = 256;
+  p.expert_offsets = static_cast<const int*>(offsets);
+  p.tile_expert = static_cast<const int*>(tile_expert);
+  p.tile_row = static_cast<const int*>(tile_row);
+  p.b_expert_stride = static_cast<long long>(hidden) * intermediate;
+  p.sb_expert_stride = static_cast<long long>(intermediate / 256) * hidden;
+  return gg::launch_simt_dtype<true>(p, tile_capacity, out_dtype, stream);
+}
+
+int gg_moe_combine(const void* expert_out, const void* weights, const void* inverse, void* out,
+                   int tokens, int top_k, int hidden, int out_dtype, void* stream_ptr) {
+  if (tokens < 0 || top_k <= 0 || hidden <= 0 || !weights || !inverse || !out ||
+      (out_dtype != GG_OUT_BF16 && out_dtype != GG_OUT_FP16)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (tokens == 0) return 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const size_t smem = static_cast<size_t>(top_k) * 8;
+  if (smem > 48 * 1024) return static_cast<int>(cudaErrorInvalidValue);
+  if (out_dtype == GG_OUT_BF16) {
+    gg::combine_kernel<__nv_bfloat16><<<tokens, 256, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(expert_out), static_cast<const float*>(weights),
+        static_cast<const int*>(inverse), static_cast<__nv_bfloat16*>(out), top_k, hidden);
+  } else {
+    gg::combine_kernel<__half><<<tokens, 256, smem, stream>>>(
+        static_cast<const __half*>(expert_out), static_cast<const float*>(weights),
+        static_cast<const int*>(inverse), static_cast<__half*>(out), top_k, hidden);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gg_device_status(int* status, void* stream_ptr) {
+  if (!status) return static_cast<int>(cudaErrorInvalidValue);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  unsigned int words[4] = {0, 0, 0, 0};
+  cudaError_t error = cudaMemcpyFromSymbolAsync(words, gg::g_device_status, sizeof(words), 0,
+                                                cudaMemcpyDeviceToHost, stream);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  error = cudaStreamSynchronize(stream);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  *status = static_cast<int>(words[0]);
+  if (words[0] != 0) {
+    const unsigned int zeros[4] = {0, 0, 0, 0};
+    error = cudaMemcpyToSymbolAsync(gg::g_device_status, zeros, sizeof(zeros), 0,
+                                    cudaMemcpyHostToDevice, stream);
+    if (error != cudaSuccess) return static_cast<int>(error);
+    error = cudaStreamSynchronize(stream);
+  }
+  return static_cast<int>(error);
+}
+
+}  // extern "C"

@@ -1,0 +1,403 @@
+// W8A8 GEMM with per-row x per-column K-group FP32 scales on the 5th-generation tensor cores.
+//
+//   C[m,n] = cast( fold over groups g = 0..Q-1, in order, starting from 0:
+//                  fmaf( float(sum_{k in g} A[m,k]*B[k,n]),  sa[m,g]*sb[g,n],  total ) )
+//
+// which is the arithmetic of the reference's portable kernel
+// (src/grain_gemm/kernels/triton.py:28-51): exact INT32 group dot, the scale product rounded
+// to FP32 once, one fused multiply-add per group, one final cast.
+//
+// Kernel shape (persistent, warp specialised, 384 threads):
+//   warp 8      TMA producer: A tile [128 rows x 128 B of K] and B tile [BN/ctas rows x 128 B]
+//               per stage, 128-byte swizzle, kStages-deep ring guarded by full/empty mbarriers.
+//   warp 9      MMA issuer: tcgen05.mma kind::i8, K = 32 per instruction, INT32 accumulators in
+//               TMEM, two accumulator buffers of BN columns.  The first MMA of every K group
+//               overwrites the buffer, the last one commits it to the promotion warps.
+//   warps 0-7   promotion: drain the group's INT32 tile with tcgen05.ld (thread = row,
+//               registers = columns), multiply by sa*sb, add into FP32 registers while the
+//               tensor core works on the next group; at the end of the tile cast and store.
+// kCtaGroup == 2 pairs two CTAs (a 2-CTA cluster) on a 256 x BN tile: each CTA loads its own
+// 128 rows of A and its own half of B, the leader CTA issues cta_group::2 MMAs that read both
+// CTAs' shared memory and write both CTAs' TMEM.
+//
+// Any M and N (rows/columns beyond the edge are zero-filled by TMA and never stored), any
+// K that is a multiple of 16 (TMA row pitch), G in {32, 64, 128, 256}; a partial last group
+// is zero-filled by TMA and uses scale index Q-1.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <type_traits>
+
+#include "ptx.cuh"
+
+namespace gg {
+
+struct GemmTcParams {
+  const float* scale_a;
+  const float* scale_b;
+  void* c;
+  int m, n, k;
+  long long sa_sm, sa_sg, sb_sg, sb_sn;
+  long long ldc;
+  int group_size;
+  int tiles_m, tiles_n;
+  int c_vector_ok;   // rows of C start on 16-byte boundaries
+  // Grouped (per-expert) mode, used by the MoE down projection; null for a plain GEMM.
+  const int* expert_offsets;   // [E+1] first sorted slot of each expert
+  const int* tile_expert;      // [tiles_m] expert of each row tile, -1 = unused
+  const int* tile_row;         // [tiles_m] first row of each row tile
+  long long b_rows_per_expert; // N (rows of the Linear weight per expert)
+  long long sb_expert_stride;  // elements between experts in scale_b
+};
+
+template <int kCtaGroup, int BN, int kStages>
+struct GemmTcShape {
+  static constexpr int kBM = 128;                       // rows per CTA
+  static constexpr int kBK = 128;                       // bytes of K per stage
+  static constexpr int kBRows = BN / kCtaGroup;         // B rows loaded by each CTA
+  static constexpr int kABytes = kBM * kBK;
+  static constexpr int kBBytes = kBRows * kBK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemColumns = 2 * BN;
+  static constexpr int kScaleBytes = 2 * BN * 4;
+  static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kBarrierBytes;
+  static constexpr int kThreads = 384;
+  static_assert(BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
+};
+
+__device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tiles_n, int& tm,
+                                                 int& tn) {
+  // Bands of eight row tiles: consecutive CTAs share B columns and a few A rows in L2.
+  const int band_size = 8 * tiles_n;
+  const int band = tile / band_size;
+  const int first_m = band * 8;
+  const int band_m = min(tiles_m - first_m, 8);
+  const int local = tile - band * band_size;
+  tm = first_m + local % band_m;
+  tn = local / band_m;
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_row_chunk(OutT* dst, const float* v, int count);
+
+// Stores up to 8 consecutive outputs; `vector` promises 16-byte alignment and count == 8.
+template <>
+__device__ __forceinline__ void store_row_chunk<float>(float* dst, const float* v, int count) {
+  for (int i = 0; i < count; ++i) dst[i] = v[i];
+}
+template <>
+__device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* dst, const float* v,
+                                                               int count) {
+  for (int i = 0; i < count; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+}
+template <>
+__device__ __forceinline__ void store_row_chunk<__half>(__half* dst, const float* v, int count) {
+  for (int i = 0; i < count; ++i) dst[i] = __float2half_rn(v[i]);
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_row_vector8(OutT* dst, const float* v) {
+  if constexpr (sizeof(OutT) == 4) {
+    float4* d = reinterpret_cast<float4*>(dst);
+    d[0] = make_float4(v[0], v[1], v[2], v[3]);
+    d[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]);
+    __nv_bfloat162 p1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]);
+    __nv_bfloat162 p3 = __floats2bfloat162_rn(v[6], v[7]);
+    uint4 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&p0);
+    packed.y = *reinterpret_cast<uint32_t*>(&p1);
+    packed.z = *reinterpret_cast<uint32_t*>(&p2);
+    packed.w = *reinterpret_cast<uint32_t*>(&p3);
+    *reinterpret_cast<uint4*>(dst) = packed;
+  } else {
+    __half2 p0 = __floats2half2_rn(v[0], v[1]);
+    __half2 p1 = __floats2half2_rn(v[2], v[3]);
+    __half2 p2 = __floats2half2_rn(v[4], v[5]);
+    __half2 p3 = __floats2half2_rn(v[6], v[7]);
+    uint4 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&p0);
+    packed.y = *reinterpret_cast<uint32_t*>(&p1);
+    packed.z = *reinterpret_cast<uint32_t*>(&p2);
+    packed.w = *reinterpret_cast<uint32_t*>(&p3);
+    *reinterpret_cast<uint4*>(dst) = packed;
+  }
+}
+
+// One promotion step over 32 drained columns: acc = fmaf(float(partial), sa*sb, acc).
+__device__ __forceinline__ void promote32(const uint32_t (&partial)[32], float sa,
+                                          const float* __restrict__ sb_smem, float* acc) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 sb = *reinterpret_cast<const float4*>(sb_smem + j);
+    const float2 s01 = mul2(make_float2(sa, sa), make_float2(sb.x, sb.y));
+    const float2 s23 = mul2(make_float2(sa, sa), make_float2(sb.z, sb.w));
+    const float2 p01 = make_float2(__int2float_rn(static_cast<int>(partial[j + 0])),
+                                   __int2float_rn(static_cast<int>(partial[j + 1])));
+    const float2 p23 = make_float2(__int2float_rn(static_cast<int>(partial[j + 2])),
+                                   __int2float_rn(static_cast<int>(partial[j + 3])));
+    const float2 r01 = fma2(p01, s01, make_float2(acc[j + 0], acc[j + 1]));
+    const float2 r23 = fma2(p23, s23, make_float2(acc[j + 2], acc[j + 3]));
+    acc[j + 0] = r01.x;
+    acc[j + 1] = r01.y;
+    acc[j + 2] = r23.x;
+    acc[j + 3] = r23.y;
+  }
+}
+
+template <int kCtaGroup, int BN, int kStages, typename OutT, bool kGrouped>
+__global__ void __launch_bounds__(384, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const GemmTcParams p) {
+  using Shape = GemmTcShape<kCtaGroup, BN, kStages>;
+  constexpr int kNC = BN / 2;  // columns owned by one promotion thread
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stage_base = smem;
+  float* sb_ring = reinterpret_cast<float*>(smem + kStages * Shape::kStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * Shape::kStageBytes +
+                                                   Shape::kScaleBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full_bar = empty_bar + kStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
+  const int worker = blockIdx.x / kCtaGroup;
+  const int workers = gridDim.x / kCtaGroup;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int groups = (p.k + p.group_size - 1) / p.group_size;
+  const int ksteps = (p.k + 31) / 32;
+  const int slabs = (p.k + Shape::kBK - 1) / Shape::kBK;
+  const int steps_per_group = p.group_size / 32;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full_bar[i], 1);
+      mbar_init(&tmem_empty_bar[i], 8 * kCtaGroup);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 8 && lane == 0) {
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  if constexpr (kCtaGroup == 2) cluster_sync_all();
+  if (warp == 9) tmem_alloc<kCtaGroup>(tmem_holder, Shape::kTmemColumns);
+  tcgen05_fence_before();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) cluster_sync_all();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  // Warps 8-11 (producer, MMA issuer, two spares) give registers to the promotion warps.
+  if (warp >= 8) {
+  setmaxnreg_dec<56>();
+  if (warp == 8) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t sequence = 0;
+      bool ok = true;
+      for (int tile = worker; tile < total_tiles && ok; tile += workers) {
+        int tm, tn;
+        tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
+        int row_a, row_b;
+        if constexpr (kGrouped) {
+          const int expert = p.tile_expert[tm];
+          if (expert < 0) continue;
+          row_a = p.tile_row[tm] + static_cast<int>(cta_rank) * Shape::kBM;
+          row_b = expert * static_cast<int>(p.b_rows_per_expert) + tn * BN +
+                  static_cast<int>(cta_rank) * Shape::kBRows;
+        } else {
+          row_a = (tm * kCtaGroup + static_cast<int>(cta_rank)) * Shape::kBM;
+          row_b = tn * BN + static_cast<int>(cta_rank) * Shape::kBRows;
+        }
+        for (int slab = 0; slab < slabs; ++slab, ++sequence) {
+          const uint32_t stage = sequence % kStages;
+          const uint32_t phase = (sequence / kStages) & 1u;
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, kSiteProducerEmpty, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
+          uint8_t* b_dst = a_dst + Shape::kABytes;
+          if constexpr (kCtaGroup == 1) {
+            mbar_expect_tx(&full_bar[stage], Shape::kStageBytes);
+            tma_load_2d(a_dst, &map_a, &full_bar[stage], slab * Shape::kBK, row_a);
+            tma_load_2d(b_dst, &map_b, &full_bar[stage], slab * Shape::kBK, row_b);
+          } else {
+            if (cta_rank == 0) mbar_expect_tx(&full_bar[stage], 2 * Shape::kStageBytes);
+            tma_load_2d_pair(a_dst, &map_a, &full_bar[stage], slab * Shape::kBK, row_a);
+            tma_load_2d_pair(b_dst, &map_b, &full_bar[stage], slab * Shape::kBK, row_b);
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ MMA issuer
+    if (cta_rank == 0 && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_i8(Shape::kBM * kCtaGroup, BN);
+      uint32_t sequence = 0;        // smem slabs consumed
+      uint32_t group_sequence = 0;  // accumulator buffers produced
+      bool ok = true;
+      for (int tile = worker; tile < total_tiles && ok; tile += workers) {
+        if constexpr (kGrouped) {
+          int tm, tn;
+          tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
+          if (p.tile_expert[tm] < 0) continue;
+        }
+        for (int kk = 0; kk < ksteps; ++kk) {
+          const int in_slab = kk & 3;
+          const uint32_t stage = sequence % kStages;
+          if (in_slab == 0) {
+            if (!mbar_wait(&full_bar[stage], (sequence / kStages) & 1u, kSiteMmaFull,
+                           abort_flag)) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after();
+          }
+          const int in_group = kk % steps_per_group;
+          const uint32_t buffer = group_sequence & 1u;
+          if (in_group == 0) {
+            if (!mbar_wait(&tmem_empty_bar[buffer], ((group_sequence >> 1) & 1u) ^ 1u,
+                           kSiteMmaTmemEmpty, abort_flag)) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after();
+          }
+          const uint32_t a_addr = smem_u32(stage_base + stage * Shape::kStageBytes) + in_slab * 32;
+          const uint32_t b_addr = a_addr + Shape::kABytes;
+          umma_i8<kCtaGroup>(tmem_base + buffer * BN, make_smem_desc_sw128(a_addr),
+                             make_smem_desc_sw128(b_addr), idesc, in_group != 0 ? 1u : 0u);
+          const bool last_step = kk == ksteps - 1;
+          if (in_group == steps_per_group - 1 || last_step) {
+            if constexpr (kCtaGroup == 1) umma_commit(&tmem_full_bar[buffer]);
+            else umma_commit_pair(&tmem_full_bar[buffer], 3);
+            ++group_sequence;
+          }
+          if (in_slab == 3 || last_step) {
+            if constexpr (kCtaGroup == 1) umma_commit(&empty_bar[stage]);
+            else umma_commit_pair(&empty_bar[stage], 3);
+            ++sequence;
+          }
+        }
+      }
+    }
+  }
+  } else {
+    setmaxnreg_inc<216>();
+    // ------------------------------------------------------------ promotion warps
+    const int half = warp >> 2;           // which half of the BN columns
+    const int quarter = warp & 3;         // TMEM lane quarter this warp may read
+    const int tid = threadIdx.x;          // 0..255
+    const int row_in_cta = quarter * 32 + lane;
+    const int col_base = half * kNC;
+    uint32_t group_sequence = 0;
+    bool ok = true;
+    OutT* c = reinterpret_cast<OutT*>(p.c);
+    // A failed wait clears `ok` but the loops keep their shape, so that every thread still
+    // reaches every named barrier the others wait on.
+    for (int tile = worker; tile < total_tiles; tile += workers) {
+      int tm, tn;
+      tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
+      int row, row_limit;
+      const float* sb_base = p.scale_b;
+      if constexpr (kGrouped) {
+        const int expert = p.tile_expert[tm];
+        if (expert < 0) continue;
+        row = p.tile_row[tm] + static_cast<int>(cta_rank) * Shape::kBM + row_in_cta;
+        row_limit = p.expert_offsets[expert + 1];
+        sb_base += static_cast<long long>(expert) * p.sb_expert_stride;
+      } else {
+        row = (tm * kCtaGroup + static_cast<int>(cta_rank)) * Shape::kBM + row_in_cta;
+        row_limit = p.m;
+      }
+      const int n0 = tn * BN;
+      const bool row_ok = row < row_limit;
+      const int sb_col = n0 + tid;
+      const bool sb_ok = tid < BN && sb_col < p.n;
+
+      float acc[kNC];
+#pragma unroll
+      for (int i = 0; i < kNC; ++i) acc[i] = 0.0f;
+
+      // Stage the first group's column scales; later groups are prefetched one ahead.
+      if (tid < BN) sb_ring[tid] = sb_ok ? sb_base[sb_col * p.sb_sn] : 0.0f;
+      float sa_next = row_ok ? p.scale_a[row * p.sa_sm] : 0.0f;
+      named_barrier_sync(1, 256);
+
+      for (int g = 0; g < groups; ++g, ++group_sequence) {
+        const float sa = sa_next;
+        float sb_next = 0.0f;
+        if (g + 1 < groups) {
+          if (sb_ok) sb_next = sb_base[(g + 1) * p.sb_sg + sb_col * p.sb_sn];
+          if (row_ok) sa_next = p.scale_a[row * p.sa_sm + (g + 1) * p.sa_sg];
+        }
+        const uint32_t buffer = group_sequence & 1u;
+        if (ok && !mbar_wait(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
+                             kSiteEpilogueTmemFull, abort_flag)) {
+          ok = false;
+        }
+        tcgen05_fence_after();
+        const float* sb_slot = sb_ring + (g & 1) * BN + col_base;
+        const uint32_t taddr =
+            tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN + col_base;
+#pragma unroll
+        for (int chunk = 0; chunk < kNC / 32; ++chunk) {
+          if (!ok) break;
+          uint32_t partial[32];
+          tmem_ld_32x32b_x32(taddr + chunk * 32, partial);
+          tmem_ld_wait();
+          if (chunk == kNC / 32 - 1) {
+            // All of this warp's TMEM reads for the buffer are done: hand it back.
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (kCtaGroup == 1) mbar_arrive(&tmem_empty_bar[buffer]);
+              else mbar_arrive_cluster(&tmem_empty_bar[buffer], 0);
+            }
+          }
+          promote32(partial, sa, sb_slot + chunk * 32, acc + chunk * 32);
+        }
+        if (tid < BN) sb_ring[((g + 1) & 1) * BN + tid] = sb_next;
+        named_barrier_sync(1, 256);
+      }
+      if (row_ok && ok) {
+        OutT* c_row = c + static_cast<long long>(row) * p.ldc + n0 + col_base;
+        const int remaining = p.n - (n0 + col_base);
+#pragma unroll
+        for (int j = 0; j < kNC; j += 8) {
+          if (j + 8 <= remaining && p.c_vector_ok) {
+            store_row_vector8<OutT>(c_row + j, acc + j);
+          } else if (j < remaining) {
+            store_row_chunk<OutT>(c_row + j, acc + j, min(8, remaining - j));
+          }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) cluster_sync_all();
+  if (warp == 9) tmem_dealloc<kCtaGroup>(tmem_base, Shape::kTmemColumns);
+}
+
+}  // namespace gg

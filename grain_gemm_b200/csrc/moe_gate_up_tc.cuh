@@ -1,0 +1,372 @@
+// Gathered Gate/Up projection fused with output rounding, SwiGLU and G256 requantisation.
+//
+// For every sorted slot (row) of every expert and every 256-channel group of the intermediate
+// dimension I:
+//   gate/up[c] = round_out( fold_g fmaf(float(dot_i32(x[token], W1[e][c], group g)),
+//                                       scale_x[token,g] * scale_w[e,g,c], total) )
+//   h[c]      = silu(gate[c]) * up[c]                       (FP32, every operation rounded)
+//   scale     = max(max_c |h[c]|, 1e-12) / 127 ;  q[c] = clamp(nearbyint(h[c]/scale), +-127)
+// i.e. src/grain_gemm/kernels/moe.py:359-393 (ragged GEMM with SOURCE_IS_TOKEN) followed by
+// :564-601 (SwiGLU + requantisation) of the reference, without the [S, 2I] intermediate and
+// without an expert-expanded copy of x: the token rows are gathered by the sorted route index
+// straight into the swizzled shared-memory operand tile.
+//
+// Work item = (128-row tile of one expert, 256-channel group), processed as two sub-tiles of
+// 128 channels; a sub-tile is one N = 256 accumulator (128 gate + 128 up columns) in TMEM.
+//   warp 8    producer: TMA for the two weight boxes, 16-byte cp.async gather for x rows
+//   warp 9    MMA issuer (tcgen05.mma kind::i8, two TMEM buffers)
+//   warps 0-7 promotion per K group, then SwiGLU; the first sub-tile's h is parked in shared
+//             memory until the second sub-tile supplies the other half of the row maximum.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gemm_tc.cuh"
+#include "moe_route.cuh"
+#include "ptx.cuh"
+
+namespace gg {
+
+struct GateUpParams {
+  const int8_t* x;            // [T, H]
+  const float* scale_x;       // [T, H/256]
+  const float* scale_w;       // [E, H/256, 2I]
+  const long long* order;     // [S]
+  const int* expert_offsets;  // [E+1]
+  const int* tile_expert;     // [max_tiles]
+  const int* tile_row;        // [max_tiles]
+  int8_t* q;                  // [S, I]
+  float* s;                   // [S, I/256]
+  int top_k, hidden, intermediate, max_tiles, interleaved;
+};
+
+struct GateUpShape {
+  static constexpr int kStages = 3;
+  static constexpr int kABytes = 128 * 128;
+  static constexpr int kBBytes = 256 * 128;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStashPitch = 132;  // floats per parked row (128 + 4: conflict-free float4)
+  static constexpr int kStashBytes = 128 * kStashPitch * 4;
+  static constexpr int kScaleBytes = 2 * 256 * 4;
+  static constexpr int kAmaxBytes = 4 * 128 * 4;
+  static constexpr int kTokenBytes = 128 * 4;
+  static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStashBytes + kScaleBytes +
+                                    kAmaxBytes + kTokenBytes + kBarrierBytes;
+  static constexpr int kGatherLag = 2;  // slabs whose cp.async may still be in flight
+};
+
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_dst, const void* src, bool valid) {
+  const uint32_t bytes = valid ? 16u : 0u;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
+template <typename RoundT>
+__device__ __forceinline__ float round_through(float v) {
+  return static_cast<float>(cast_out<RoundT>(v));
+}
+
+template <typename RoundT>
+__global__ void __launch_bounds__(384, 1)
+moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpParams p) {
+  using Shape = GateUpShape;
+  constexpr int kStages = Shape::kStages;
+  constexpr int BN = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stage_base = smem;
+  float* stash = reinterpret_cast<float*>(smem + kStages * Shape::kStageBytes);
+  float* sb_ring = stash + 128 * Shape::kStashPitch;
+  float* amax_part = sb_ring + 2 * BN;
+  int* tile_tokens = reinterpret_cast<int*>(amax_part + 4 * 128);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tile_tokens + 128);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full_bar = empty_bar + kStages;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int channel_groups = p.intermediate / 256;
+  const int total_items = p.max_tiles * channel_groups;
+  const int groups = p.hidden / 256;
+  const int slabs = p.hidden / 128;
+  const int ksteps = p.hidden / 32;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full_bar[i], 33);  // 32 gather lanes + the TMA transaction arrival
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full_bar[i], 1);
+      mbar_init(&tmem_empty_bar[i], 8);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 8 && lane == 0) prefetch_tensormap(&map_w);
+  if (warp == 9) tmem_alloc<1>(tmem_holder, 512);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  // Warps 8-11 (producer, MMA issuer, two spares) give registers to the promotion warps.
+  if (warp >= 8) {
+  setmaxnreg_dec<56>();
+  if (warp == 8) {
+    // ------------------------------------------------------------ producer
+    uint32_t sequence = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int tile = item / channel_groups;
+      const int jg = item - tile * channel_groups;
+      const int expert = p.tile_expert[tile];
+      if (expert < 0) continue;
+      const int row0 = p.tile_row[tile];
+      const int row_end = p.expert_offsets[expert + 1];
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = lane + 32 * i;
+        const int row = row0 + r;
+        tile_tokens[r] = row < row_end ? static_cast<int>(p.order[row] / p.top_k) : -1;
+      }
+      __syncwarp();
+      for (int sub = 0; sub < 2 && ok; ++sub) {
+        const int channel0 = jg * 256 + sub * 128;
+        const int w_base = expert * 2 * p.intermediate;
+        const int row_gate = p.interleaved ? w_base + 2 * channel0 : w_base + channel0;
+        const int row_up = p.interleaved ? row_gate + 128 : w_base + p.intermediate + channel0;
+        for (int slab = 0; slab < slabs; ++slab, ++sequence) {
+          const uint32_t stage = sequence % kStages;
+          // All 32 lanes wait; the vote keeps the warp's control flow uniform on failure.
+          const bool got = mbar_wait(&empty_bar[stage], ((sequence / kStages) & 1u) ^ 1u,
+                                     kSiteProducerEmpty, abort_flag);
+          if (!__all_sync(0xffffffffu, got)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
+          uint8_t* b_dst = a_dst + Shape::kABytes;
+          if (lane == 0) {
+            mbar_expect_tx(&full_bar[stage], Shape::kBBytes);
+            tma_load_2d(b_dst, &map_w, &full_bar[stage], slab * 128, row_gate);
+            tma_load_2d(b_dst + 128 * 128, &map_w, &full_bar[stage], slab * 128, row_up);
+          }
+          const uint32_t a_smem = smem_u32(a_dst);
+          const int chunk = lane & 7;
+#pragma unroll 8
+          for (int i = 0; i < 32; ++i) {
+            const int r = (lane >> 3) + 4 * i;
+            const int token = tile_tokens[r];
+            const int8_t* src = p.x + (token >= 0 ? static_cast<long long>(token) * p.hidden : 0) +
+                                slab * 128 + chunk * 16;
+            cp_async_16_zfill(a_smem + r * 128 + ((chunk ^ (r & 7)) << 4), src, token >= 0);
+          }
+          cp_async_commit();
+          if (sequence >= Shape::kGatherLag) {
+            cp_async_wait<Shape::kGatherLag>();
+            fence_proxy_async();
+            mbar_arrive(&full_bar[(sequence - Shape::kGatherLag) % kStages]);
+          }
+        }
+      }
+    }
+    // Publish the slabs whose copies were still in flight.
+    cp_async_wait<0>();
+    fence_proxy_async();
+    if (ok) {
+      const uint32_t first = sequence >= Shape::kGatherLag ? sequence - Shape::kGatherLag : 0;
+      for (uint32_t q = first; q < sequence; ++q) mbar_arrive(&full_bar[q % kStages]);
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_i8(128, BN);
+      uint32_t sequence = 0, group_sequence = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const int tile = item / channel_groups;
+        if (p.tile_expert[tile] < 0) continue;
+        for (int sub = 0; sub < 2 && ok; ++sub) {
+          for (int kk = 0; kk < ksteps; ++kk) {
+            const int in_slab = kk & 3;
+            const uint32_t stage = sequence % kStages;
+            if (in_slab == 0) {
+              if (!mbar_wait(&full_bar[stage], (sequence / kStages) & 1u, kSiteMmaFull,
+                             abort_flag)) {
+                ok = false;
+                break;
+              }
+              tcgen05_fence_after();
+            }
+            const int in_group = kk & 7;
+            const uint32_t buffer = group_sequence & 1u;
+            if (in_group == 0) {
+              if (!mbar_wait(&tmem_empty_bar[buffer], ((group_sequence >> 1) & 1u) ^ 1u,
+                             kSiteMmaTmemEmpty, abort_flag)) {
+                ok = false;
+                break;
+              }
+              tcgen05_fence_after();
+            }
+            const uint32_t a_addr = smem_u32(stage_base + stage * Shape::kStageBytes) + in_slab * 32;
+            const uint32_t b_addr = a_addr + Shape::kABytes;
+            umma_i8<1>(tmem_base + buffer * BN, make_smem_desc_sw128(a_addr),
+                       make_smem_desc_sw128(b_addr), idesc, in_group != 0 ? 1u : 0u);
+            if (in_group == 7) {
+              umma_commit(&tmem_full_bar[buffer]);
+              ++group_sequence;
+            }
+            if (in_slab == 3) {
+              umma_commit(&empty_bar[stage]);
+              ++sequence;
+            }
+          }
+        }
+      }
+    }
+  }
+  } else {
+    setmaxnreg_inc<216>();
+    // ------------------------------------------------------------ promotion + SwiGLU warps
+    const int half = warp >> 2;
+    const int quarter = warp & 3;
+    const int tid = threadIdx.x;
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t group_sequence = 0;
+    bool ok = true;
+    float* stash_row = stash + row_in_tile * Shape::kStashPitch + half * 64;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      const int tile = item / channel_groups;
+      const int jg = item - tile * channel_groups;
+      const int expert = p.tile_expert[tile];
+      if (expert < 0) continue;
+      const int row = p.tile_row[tile] + row_in_tile;
+      const bool row_ok = row < p.expert_offsets[expert + 1];
+      const long long token = row_ok ? p.order[row] / p.top_k : 0;
+      const float* sa_row = p.scale_x + token * groups;
+      const float* sb_base = p.scale_w + static_cast<long long>(expert) * groups * 2 * p.intermediate;
+      float amax_first = 0.0f;
+
+      for (int sub = 0; sub < 2; ++sub) {
+        const int channel0 = jg * 256 + sub * 128;
+        // Accumulator column `tid` of this sub-tile corresponds to this weight column.
+        const int sb_col = p.interleaved ? 2 * channel0 + tid
+                                         : (tid < 128 ? channel0 + tid
+                                                      : p.intermediate + channel0 + tid - 128);
+        float acc[128];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+        sb_ring[tid] = sb_base[sb_col];
+        float sa_next = row_ok ? sa_row[0] : 0.0f;
+        named_barrier_sync(1, 256);
+
+        for (int g = 0; g < groups; ++g, ++group_sequence) {
+          const float sa = sa_next;
+          float sb_next = 0.0f;
+          if (g + 1 < groups) {
+            sb_next = sb_base[static_cast<long long>(g + 1) * 2 * p.intermediate + sb_col];
+            if (row_ok) sa_next = sa_row[g + 1];
+          }
+          const uint32_t buffer = group_sequence & 1u;
+          if (ok && !mbar_wait(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
+                               kSiteEpilogueTmemFull, abort_flag)) {
+            ok = false;
+          }
+          tcgen05_fence_after();
+          const float* sb_slot = sb_ring + (g & 1) * BN;
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN;
+#pragma unroll
+          for (int chunk = 0; chunk < 4; ++chunk) {
+            if (!ok) break;
+            // Split layout: chunks 0,1 are this thread's gate columns, 2,3 its up columns.
+            const int column = p.interleaved ? half * 128 + chunk * 32
+                                             : (chunk >> 1) * 128 + half * 64 + (chunk & 1) * 32;
+            uint32_t partial[32];
+            tmem_ld_32x32b_x32(taddr + column, partial);
+            tmem_ld_wait();
+            if (chunk == 3) {
+              tcgen05_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
+            }
+            promote32(partial, sa, sb_slot + column, acc + chunk * 32);
+          }
+          sb_ring[((g + 1) & 1) * BN + tid] = sb_next;
+          named_barrier_sync(1, 256);
+        }
+
+        // SwiGLU on the rounded gate/up values; h overwrites acc[0..63].
+        float amax = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const float gate = round_through<RoundT>(p.interleaved ? acc[2 * c] : acc[c]);
+          const float up = round_through<RoundT>(p.interleaved ? acc[2 * c + 1] : acc[64 + c]);
+          const float h = swiglu_value(gate, up);
+          acc[c] = h;
+          amax = fmaxf(amax, fabsf(h));
+        }
+        amax_part[(sub * 2 + half) * 128 + row_in_tile] = amax;
+        if (sub == 0) {
+#pragma unroll
+          for (int c = 0; c < 64; c += 4)
+            *reinterpret_cast<float4*>(stash_row + c) =
+                make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
+          amax_first = amax;
+        } else {
+          named_barrier_sync(1, 256);
+          float row_max = fmaxf(amax, amax_first);
+          row_max = fmaxf(row_max, amax_part[(0 * 2 + (half ^ 1)) * 128 + row_in_tile]);
+          row_max = fmaxf(row_max, amax_part[(1 * 2 + (half ^ 1)) * 128 + row_in_tile]);
+          const float scale = quantize_scale(row_max);
+          if (row_ok && ok) {
+            int8_t* q_row = p.q + static_cast<long long>(row) * p.intermediate + jg * 256;
+#pragma unroll
+            for (int piece = 0; piece < 2; ++piece) {
+              // piece 0: parked first sub-tile (channels half*64..), piece 1: registers.
+              uint4* dst = reinterpret_cast<uint4*>(q_row + piece * 128 + half * 64);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint32_t words[4];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                  uint32_t packed = 0;
+#pragma unroll
+                  for (int b = 0; b < 4; ++b) {
+                    const int c = v * 16 + w * 4 + b;
+                    const float h = piece == 0 ? stash_row[c] : acc[c];
+                    packed |= (static_cast<uint32_t>(quantize_value(h, scale)) & 0xffu) << (8 * b);
+                  }
+                  words[w] = packed;
+                }
+                dst[v] = make_uint4(words[0], words[1], words[2], words[3]);
+              }
+            }
+            if (half == 0) p.s[static_cast<long long>(row) * channel_groups + jg] = scale;
+          }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc<1>(tmem_base, 512);
+}
+
+}  // namespace gg

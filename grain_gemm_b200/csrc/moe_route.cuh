@@ -1,0 +1,322 @@
+// MoE routing metadata, SwiGLU requantisation and top-k combine kernels.
+//
+// Routing restates src/grain_gemm/kernels/moe.py:48-171,222-291 of the reference as a stable
+// counting sort: key = expert id when the token is enabled and 0 <= id < E (tested at the
+// ids' own width, so INT64 ids cannot wrap), else E; `order` lists all assignments sorted by
+// key with ties in original order (invalid tail included); `inverse` is the sorted slot or
+// -1; counts/offsets per expert; statistics = (enabled out-of-range ids, max count, total).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gemm_simt.cuh"
+#include "ptx.cuh"
+
+namespace gg {
+
+constexpr int kRouteChunk = 1024;
+
+struct RouteParams {
+  const void* ids;
+  int ids_are_i64;
+  const uint8_t* mask;  // [T] or null
+  int tokens, top_k, experts;
+  void* effective_ids;  // same width as ids
+  long long* order;     // [S]
+  int* inverse;         // [S]
+  int* counts;          // [E]
+  int* offsets;         // [E+1]
+  int* statistics;      // [3]
+  int* workspace;       // [chunks * (E + 1) + chunks] for the multi-chunk path
+};
+
+__device__ __forceinline__ int route_key(const RouteParams& p, long long s, bool& invalid) {
+  const long long id = p.ids_are_i64 ? reinterpret_cast<const long long*>(p.ids)[s]
+                                     : static_cast<long long>(reinterpret_cast<const int*>(p.ids)[s]);
+  const bool enabled = p.mask == nullptr || p.mask[s / p.top_k] != 0;
+  const bool in_range = id >= 0 && id < p.experts;
+  invalid = enabled && !in_range;
+  const int key = (enabled && in_range) ? static_cast<int>(id) : p.experts;
+  if (p.ids_are_i64) reinterpret_cast<long long*>(p.effective_ids)[s] = key;
+  else reinterpret_cast<int*>(p.effective_ids)[s] = key;
+  return key;
+}
+
+// Stable placement of one chunk: `cursor[key]` holds the next free slot of each key for this
+// chunk; warps take turns in index order, lanes of a warp rank themselves among equal keys.
+__device__ __forceinline__ void route_place_chunk(const RouteParams& p, long long s, bool present,
+                                                  int key, int* cursor) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int turn = 0; turn < kRouteChunk / 32; ++turn) {
+    if (warp == turn) {
+      const unsigned active = __ballot_sync(0xffffffffu, present);
+      if (present) {
+        const unsigned same = __match_any_sync(active, key);
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        const int leader = __ffs(same) - 1;
+        int first = 0;
+        if (lane == leader) {
+          first = cursor[key];
+          cursor[key] = first + __popc(same);
+        }
+        first = __shfl_sync(same, first, leader);
+        const int slot = first + rank;
+        p.order[slot] = s;
+        p.inverse[s] = key < p.experts ? slot : -1;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Scan of the per-key totals held in bins[0..E]; leaves bins[key] = first slot of the key and
+// writes counts, offsets and statistics.  Called by one thread.
+__device__ __forceinline__ void route_finish_totals(const RouteParams& p, int* bins, int invalid) {
+  int running = 0, maximum = 0;
+  p.offsets[0] = 0;
+  for (int e = 0; e <= p.experts; ++e) {
+    const int count = bins[e];
+    bins[e] = running;
+    running += count;
+    if (e < p.experts) {
+      p.counts[e] = count;
+      p.offsets[e + 1] = running;
+      maximum = max(maximum, count);
+    }
+  }
+  p.statistics[0] = invalid;
+  p.statistics[1] = maximum;
+  p.statistics[2] = p.offsets[p.experts];
+}
+
+// Whole routing problem in one CTA (S <= 1024): keys, histogram, scan and placement.
+__global__ void __launch_bounds__(kRouteChunk) route_single_kernel(const RouteParams p) {
+  extern __shared__ int bins[];  // [E + 2]; the last entry counts invalid ids
+  const long long slots = static_cast<long long>(p.tokens) * p.top_k;
+  for (int i = threadIdx.x; i < p.experts + 2; i += blockDim.x) bins[i] = 0;
+  __syncthreads();
+  const long long s = threadIdx.x;
+  const bool present = s < slots;
+  int key = p.experts;
+  if (present) {
+    bool invalid;
+    key = route_key(p, s, invalid);
+    atomicAdd(&bins[key], 1);
+    if (invalid) atomicAdd(&bins[p.experts + 1], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) route_finish_totals(p, bins, bins[p.experts + 1]);
+  __syncthreads();
+  route_place_chunk(p, s, present, key, bins);
+}
+
+__global__ void __launch_bounds__(kRouteChunk) route_histogram_kernel(const RouteParams p) {
+  extern __shared__ int bins[];
+  const long long slots = static_cast<long long>(p.tokens) * p.top_k;
+  const int chunks = gridDim.x;
+  for (int i = threadIdx.x; i < p.experts + 2; i += blockDim.x) bins[i] = 0;
+  __syncthreads();
+  const long long s = static_cast<long long>(blockIdx.x) * kRouteChunk + threadIdx.x;
+  if (s < slots) {
+    bool invalid;
+    const int key = route_key(p, s, invalid);
+    atomicAdd(&bins[key], 1);
+    if (invalid) atomicAdd(&bins[p.experts + 1], 1);
+  }
+  __syncthreads();
+  int* histogram = p.workspace + static_cast<long long>(blockIdx.x) * (p.experts + 1);
+  for (int i = threadIdx.x; i <= p.experts; i += blockDim.x) histogram[i] = bins[i];
+  if (threadIdx.x == 0) p.workspace[static_cast<long long>(chunks) * (p.experts + 1) + blockIdx.x] =
+      bins[p.experts + 1];
+}
+
+// One CTA: turns the per-chunk histograms into per-chunk first slots (in place).
+__global__ void __launch_bounds__(1024) route_scan_kernel(const RouteParams p, int chunks) {
+  extern __shared__ int bins[];  // [E + 1]
+  const int stride = p.experts + 1;
+  for (int key = threadIdx.x; key <= p.experts; key += blockDim.x) {
+    int total = 0;
+    for (int c = 0; c < chunks; ++c) total += p.workspace[static_cast<long long>(c) * stride + key];
+    bins[key] = total;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int invalid = 0;
+    const int* invalid_counts = p.workspace + static_cast<long long>(chunks) * stride;
+    for (int c = 0; c < chunks; ++c) invalid += invalid_counts[c];
+    route_finish_totals(p, bins, invalid);
+  }
+  __syncthreads();
+  for (int key = threadIdx.x; key <= p.experts; key += blockDim.x) {
+    int running = bins[key];
+    for (int c = 0; c < chunks; ++c) {
+      int* cell = p.workspace + static_cast<long long>(c) * stride + key;
+      const int count = *cell;
+      *cell = running;
+      running += count;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kRouteChunk) route_place_kernel(const RouteParams p) {
+  extern __shared__ int bins[];
+  const long long slots = static_cast<long long>(p.tokens) * p.top_k;
+  const int* first = p.workspace + static_cast<long long>(blockIdx.x) * (p.experts + 1);
+  for (int i = threadIdx.x; i <= p.experts; i += blockDim.x) bins[i] = first[i];
+  __syncthreads();
+  const long long s = static_cast<long long>(blockIdx.x) * kRouteChunk + threadIdx.x;
+  const bool present = s < slots;
+  int key = p.experts;
+  if (present) {
+    key = p.ids_are_i64 ? static_cast<int>(reinterpret_cast<const long long*>(p.effective_ids)[s])
+                        : reinterpret_cast<const int*>(p.effective_ids)[s];
+  }
+  route_place_chunk(p, s, present, key, bins);
+}
+
+// Row-tile list for the grouped kernels: every expert's sorted rows are cut into tiles of
+// `tile_rows`; tile_expert/tile_row have room for ceil(S / tile_rows) + E entries, unused
+// entries get expert -1.  One CTA.
+__global__ void __launch_bounds__(1024)
+moe_tiles_kernel(const int* __restrict__ offsets, int experts, int tile_rows, int max_tiles,
+                 int* __restrict__ tile_expert, int* __restrict__ tile_row) {
+  extern __shared__ int first_tile[];  // [E + 1]
+  if (threadIdx.x == 0) {
+    int running = 0;
+    for (int e = 0; e < experts; ++e) {
+      first_tile[e] = running;
+      running += (offsets[e + 1] - offsets[e] + tile_rows - 1) / tile_rows;
+    }
+    first_tile[experts] = running;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int begin = offsets[e];
+    for (int t = first_tile[e]; t < first_tile[e + 1]; ++t) {
+      tile_expert[t] = e;
+      tile_row[t] = begin + (t - first_tile[e]) * tile_rows;
+    }
+  }
+  for (int t = first_tile[experts] + threadIdx.x; t < max_tiles; t += blockDim.x) {
+    tile_expert[t] = -1;
+    tile_row[t] = 0;
+  }
+}
+
+// ------------------------------------------------------------------ SwiGLU + requantisation
+
+// h = silu(gate) * up with every operation rounded separately (no FMA contraction), as in
+// src/grain_gemm/kernels/moe.py:594 of the reference (div_rn(g, 1 + exp(-g)) * u).
+__device__ __forceinline__ float swiglu_value(float gate, float up) {
+  const float denominator = __fadd_rn(1.0f, expf(-gate));
+  return __fmul_rn(__fdiv_rn(gate, denominator), up);
+}
+
+// q = clamp(nearbyint(h / scale), -127, 127) with scale = max(amax, 1e-12) / 127
+// (src/grain_gemm/kernels/moe.py:321-328).
+__device__ __forceinline__ float quantize_scale(float amax) {
+  return __fdiv_rn(fmaxf(amax, 1.0e-12f), 127.0f);
+}
+__device__ __forceinline__ int quantize_value(float h, float scale) {
+  const float rounded = nearbyintf(__fdiv_rn(h, scale));
+  return static_cast<int>(fminf(fmaxf(rounded, -127.0f), 127.0f));
+}
+
+// Stand-alone SwiGLU + G256 requantisation over a [rows, 2I] gate/up matrix (the unfused
+// path).  One warp per (row, 256-channel group); rows at or beyond *valid_rows get q = 0 and
+// scale = 1e-12/127.
+template <typename InT>
+__global__ void __launch_bounds__(256)
+swiglu_quantize_kernel(const InT* __restrict__ gate_up, long long rows,
+                       const int* __restrict__ valid_rows_ptr, int intermediate, int interleaved,
+                       int8_t* __restrict__ q, float* __restrict__ s) {
+  const int groups = intermediate / 256;
+  const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (item >= rows * groups) return;
+  const long long row = item / groups;
+  const int group = static_cast<int>(item - row * groups);
+  const int lane = threadIdx.x & 31;
+  const long long valid_rows = valid_rows_ptr ? *valid_rows_ptr : rows;
+  int8_t* q_row = q + row * intermediate + group * 256;
+  if (row >= valid_rows) {
+    for (int j = lane; j < 256; j += 32) q_row[j] = 0;
+    if (lane == 0) s[row * groups + group] = __fdiv_rn(1.0e-12f, 127.0f);
+    return;
+  }
+  const InT* in = gate_up + row * 2 * intermediate;
+  float h[8];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int channel = group * 256 + i * 32 + lane;
+    const float gate = static_cast<float>(in[interleaved ? 2 * channel : channel]);
+    const float up = static_cast<float>(in[interleaved ? 2 * channel + 1 : intermediate + channel]);
+    h[i] = swiglu_value(gate, up);
+    amax = fmaxf(amax, fabsf(h[i]));
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1)
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+  const float scale = quantize_scale(amax);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q_row[i * 32 + lane] = static_cast<int8_t>(quantize_value(h[i], scale));
+  if (lane == 0) s[row * groups + group] = scale;
+}
+
+// ------------------------------------------------------------------ top-k combine
+
+// out[t,:] = cast( sum over the token's slots r, in slot order, with inverse >= 0 of
+//                  float(expert_out[inverse[t*R+r], :]) * weights[t,r] )
+// product and sum are separate FP32 operations (src/grain_gemm/kernels/moe.py:634-653).
+// One CTA per token, 8 columns per thread per step.
+template <typename T>
+__global__ void __launch_bounds__(256)
+combine_kernel(const T* __restrict__ expert_out, const float* __restrict__ weights,
+               const int* __restrict__ inverse, T* __restrict__ out, int top_k, int hidden) {
+  extern __shared__ int slot_smem[];  // [R] slots then [R] weights
+  float* weight_smem = reinterpret_cast<float*>(slot_smem + top_k);
+  const long long token = blockIdx.x;
+  for (int r = threadIdx.x; r < top_k; r += blockDim.x) {
+    const int slot = inverse[token * top_k + r];
+    slot_smem[r] = slot;
+    weight_smem[r] = slot >= 0 ? weights[token * top_k + r] : 0.0f;
+  }
+  __syncthreads();
+  const bool vector_ok = (hidden % 8) == 0;
+  if (vector_ok) {
+    for (int col = threadIdx.x * 8; col < hidden; col += blockDim.x * 8) {
+      float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < top_k; ++r) {
+        const int slot = slot_smem[r];
+        if (slot < 0) continue;
+        const float w = weight_smem[r];
+        const uint4 packed =
+            *reinterpret_cast<const uint4*>(expert_out + static_cast<long long>(slot) * hidden + col);
+        const T* values = reinterpret_cast<const T*>(&packed);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          total[i] = __fadd_rn(total[i], __fmul_rn(static_cast<float>(values[i]), w));
+      }
+      uint4 packed_out;
+      T* outputs = reinterpret_cast<T*>(&packed_out);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) outputs[i] = cast_out<T>(total[i]);
+      *reinterpret_cast<uint4*>(out + token * hidden + col) = packed_out;
+    }
+  } else {
+    for (int col = threadIdx.x; col < hidden; col += blockDim.x) {
+      float total = 0.0f;
+      for (int r = 0; r < top_k; ++r) {
+        const int slot = slot_smem[r];
+        if (slot < 0) continue;
+        total = __fadd_rn(total, __fmul_rn(static_cast<float>(
+                                               expert_out[static_cast<long long>(slot) * hidden + col]),
+                                           weight_smem[r]));
+      }
+      out[token * hidden + col] = cast_out<T>(total);
+    }
+  }
+}
+
+}  // namespace gg

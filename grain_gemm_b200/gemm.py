@@ -1,0 +1,164 @@
+"""W8A8 GEMM with per-row x per-column K-group scales: the ``grain_gemm.int8_gemm`` API on B200.
+
+Same signature, validation order, exception types and messages as the reference's
+``src/grain_gemm/gemm.py`` (``_validate`` :13-50, ``get_kernel_config`` :84-178, ``int8_gemm``
+:181-220 there).  The dispatch collapses to one backend: hand-written sm_100a CUDA behind the
+C ABI of ``libgrain_b200.so``.  There is no Triton path and no CPU fallback.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _loader
+
+_BACKENDS = ("auto", "cuda")
+_FOREIGN_BACKENDS = ("triton", "cutlass")
+
+
+def _check_backend(backend):
+    if backend in _FOREIGN_BACKENDS:
+        raise ValueError(f"backend='{backend}' does not exist in the B200 build; "
+                         "use 'auto' or 'cuda' (hand-written sm_100a kernels)")
+    if backend not in _BACKENDS:
+        raise ValueError("backend must be 'auto', 'triton', 'cuda', or 'cutlass'")
+
+
+def _validate(a, b, scale_a, scale_b, group_size, output_dtype):
+    if type(group_size) is not int or group_size not in (32, 64, 128, 256):
+        raise ValueError("group_size must be one of 32, 64, 128, or 256")
+    if output_dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise TypeError("output_dtype must be torch.float32, torch.float16, or torch.bfloat16")
+    tensors = (("a", a), ("b", b), ("scale_a", scale_a), ("scale_b", scale_b))
+    for name, tensor in tensors:
+        if not isinstance(tensor, torch.Tensor):
+            raise TypeError(f"{name} must be a torch.Tensor")
+        if tensor.layout != torch.strided or tensor.ndim != 2:
+            raise ValueError(f"{name} must be a two-dimensional strided tensor")
+        expected = torch.int8 if name in ("a", "b") else torch.float32
+        if tensor.dtype != expected:
+            raise TypeError(f"{name} must have dtype {expected}")
+    m, k = a.shape
+    n = b.shape[1]
+    if b.shape[0] != k:
+        raise ValueError("a.shape[1] must equal b.shape[0] (the K dimension)")
+    groups = (k + group_size - 1) // group_size
+    for name, tensor, shape in (("scale_a", scale_a, (m, groups)),
+                                ("scale_b", scale_b, (groups, n))):
+        if tensor.shape != shape:
+            raise ValueError(f"{name} must have shape {shape}, got {tuple(tensor.shape)}")
+    for name, tensor in tensors:
+        if tensor.device != a.device:
+            raise ValueError(f"{name} must be on the same device as a ({a.device})")
+        if tensor.device.type != "cuda":
+            raise ValueError(f"{name} must be a CUDA tensor")
+        if tensor.numel() and any(s <= 0 for s in tensor.stride()):
+            raise ValueError(f"{name} must have positive strides")
+        if tensor.numel() and sum((d - 1) * s for d, s in zip(tensor.shape, tensor.stride())) > 2**31 - 1:
+            raise ValueError(f"{name} exceeds the supported 32-bit relative element offsets")
+    if m * n > 2**31:
+        raise ValueError("output exceeds the supported 32-bit relative element offsets")
+    if torch.cuda.get_device_capability(a.device) != (10, 0):
+        raise ValueError("this build of GrainGEMM requires an NVIDIA B200 (sm_100) GPU")
+    return m, n, k
+
+
+def _operand_strides(a, b):
+    """Element strides of A [M,K] and B [K,N]; a dimension of size one is never stepped
+    through, so its stride is replaced by one the tensor-core path accepts."""
+    m, k = a.shape
+    n = b.shape[1]
+    a_sm, a_sk = a.stride()
+    b_sk, b_sn = b.stride()
+    if k == 1:
+        a_sk = b_sk = 1
+    if m == 1:
+        a_sm = -(-(k * a_sk) // 16) * 16
+    if n == 1:
+        b_sn = -(-(k * b_sk) // 16) * 16
+    return a_sm, a_sk, b_sk, b_sn
+
+
+def _select(a, b, result, group_size, output_dtype):
+    m, k = a.shape
+    n = b.shape[1]
+    return _loader.library().gg_int8_gemm_select(
+        _loader.pointer(a), _loader.pointer(b), _loader.pointer(result), m, n, k,
+        *_operand_strides(a, b),
+        result.stride(0) if result is not None else n,
+        group_size, _loader.OUT_DTYPE[output_dtype])
+
+
+def get_kernel_config(a, b, *, group_size=256, output_dtype=torch.bfloat16,
+                      scale_a=None, scale_b=None, backend="auto"):
+    """Describe the kernel ``int8_gemm`` would launch, without launching it.
+
+    Returns a dict with ``policy``, ``compute_capability``, ``backend`` and the
+    tile description (``variant``, ``block_m``, ``block_n``, ``cta_group``), like the
+    reference's ``get_kernel_config`` does for its own backends.
+    """
+    _check_backend(backend)
+    capability = torch.cuda.get_device_capability(a.device)
+    with torch.cuda.device(a.device):
+        variant = _select(a, b, None, group_size, output_dtype)
+    name = _loader.VARIANT_NAMES[variant]
+    pair = name.startswith("tc_pair")
+    block_n = int(name.rsplit("n", 1)[1]) if name.startswith("tc") else 32
+    return dict(policy="sm100_native", compute_capability=list(capability), backend="cuda",
+                variant=name, block_m=(256 if pair else 128) if name.startswith("tc") else 32,
+                block_n=block_n, cta_group=2 if pair else 1,
+                tensor_cores=name.startswith("tc"))
+
+
+def launch(a, b, scale_a, scale_b, out, group_size, variant="auto"):
+    """Launch the GEMM on torch's current stream (arguments already validated)."""
+    m, k = a.shape
+    n = b.shape[1]
+    status = _loader.library().gg_int8_gemm(
+        _loader.pointer(a), _loader.pointer(b), _loader.pointer(scale_a), _loader.pointer(scale_b),
+        _loader.pointer(out), m, n, k,
+        *_operand_strides(a, b),
+        scale_a.stride(0), scale_a.stride(1), scale_b.stride(0), scale_b.stride(1),
+        out.stride(0), group_size, _loader.OUT_DTYPE[out.dtype], _loader.VARIANTS[variant],
+        _loader.stream_pointer(a.device))
+    _loader.check(status, "gg_int8_gemm")
+    return out
+
+
+def int8_gemm(a, b, scale_a, scale_b, *, group_size=256,
+              output_dtype=torch.bfloat16, backend="auto", variant="auto"):
+    """Compute INT8 A[M,K] @ B[K,N] with independent row/column K-group scales.
+
+    FP32 scale shapes are [M, ceil(K/G)] and [ceil(K/G), N].  Each G-element dot product
+    accumulates in INT32, then contributes to an FP32 scaled sum by one fused multiply-add
+    per group; the result is cast once to BF16 (default), FP16 or FP32.  G can be
+    32/64/128/256.  Positive-stride views and M/N/K tails are supported without packing:
+    operands whose K direction is contiguous and 16-byte aligned run on the tensor cores,
+    everything else on a CUDA-core kernel with identical arithmetic.  ``variant`` pins a
+    kernel variant (see ``_loader.VARIANTS``) and is meant for tests and benchmarks.
+    """
+    _check_backend(backend)
+    m, n, k = _validate(a, b, scale_a, scale_b, group_size, output_dtype)
+    with torch.cuda.device(a.device):
+        if m == 0 or n == 0 or k == 0:
+            return torch.zeros((m, n), device=a.device, dtype=output_dtype)
+        result = torch.empty((m, n), device=a.device, dtype=output_dtype)
+        launch(a, b, scale_a, scale_b, result, group_size, variant)
+    return result
+
+
+def int8_gemm_partials(a, b, scale_a, scale_b, *, group_size=256):
+    """Test aid: FP32 result and the INT32 group dots ``[M, N, ceil(K/G)]`` (CUDA cores)."""
+    m, n, k = _validate(a, b, scale_a, scale_b, group_size, torch.float32)
+    groups = (k + group_size - 1) // group_size
+    with torch.cuda.device(a.device):
+        result = torch.empty((m, n), device=a.device, dtype=torch.float32)
+        partials = torch.empty((m, n, groups), device=a.device, dtype=torch.int32)
+        status = _loader.library().gg_int8_gemm_partials(
+            _loader.pointer(a), _loader.pointer(b), _loader.pointer(scale_a),
+            _loader.pointer(scale_b), _loader.pointer(result), _loader.pointer(partials), m, n, k,
+            a.stride(0), a.stride(1), b.stride(0), b.stride(1),
+            scale_a.stride(0), scale_a.stride(1), scale_b.stride(0), scale_b.stride(1),
+            group_size, _loader.stream_pointer(a.device))
+        _loader.check(status, "gg_int8_gemm_partials")
+    return result, partials

@@ -1,0 +1,155 @@
+/*
+ * C ABI of libgrain_b200.so: the B200 (sm_100a) implementation of GrainGEMM's two hot
+ * paths, the W8A8 K-group-scaled GEMM and the inference MoE FFN stages.
+ *
+ * Conventions (the reference's, src/grain_gemm/kernels/csrc/sm110/int8_g256_moe_gather.cu:380-440):
+ *  - plain pointers and sizes only; every pointer is device memory of the current device
+ *    unless stated otherwise; the caller owns all memory, outputs and workspaces included;
+ *  - every launch goes to `stream` (a cudaStream_t passed as void*); no entry point
+ *    synchronises, allocates or keeps state between calls, except where stated;
+ *  - return value: 0 = success; > 0 = cudaError_t; -10000 - r = CUresult r from the tensor-map
+ *    encoder; gg_error_string() decodes all of them.
+ * Paths quoted below are relative to the reference project.
+ */
+#ifndef GRAIN_GEMM_B200_H
+#define GRAIN_GEMM_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Output element types. */
+#define GG_OUT_FP32 0
+#define GG_OUT_BF16 1
+#define GG_OUT_FP16 2
+
+/* Kernel variants for gg_int8_gemm (GG_VARIANT_AUTO picks by layout and shape). */
+#define GG_VARIANT_AUTO 0
+#define GG_VARIANT_SIMT 1        /* CUDA-core kernel: any strides, any K */
+#define GG_VARIANT_TC_N256 2     /* tcgen05, one CTA per 128 x 256 tile */
+#define GG_VARIANT_TC_N128 3     /* tcgen05, one CTA per 128 x 128 tile */
+#define GG_VARIANT_TC_N64 4      /* tcgen05, one CTA per 128 x 64 tile */
+#define GG_VARIANT_TC_PAIR_N256 5 /* tcgen05 cta_group::2, CTA pair per 256 x 256 tile */
+#define GG_VARIANT_TC_PAIR_N128 6 /* tcgen05 cta_group::2, CTA pair per 256 x 128 tile */
+
+/* ABI version of this header; the Python loader refuses a library that reports another. */
+int gg_abi_version(void);
+
+/* Text for a status returned by any entry point.  Replaces grain_cuda_error_string /
+ * grain_moe_gather_error_string (csrc/sm110/int8_g256_cute.cu:300, int8_g256_moe_gather.cu:437). */
+const char* gg_error_string(int status);
+
+/*
+ * C[M,N] = A[M,K] @ B[K,N] with FP32 scales scale_a[M, ceil(K/G)] and scale_b[ceil(K/G), N]:
+ * exact INT32 dot per K group, then total = fmaf(float(dot), sa*sb, total) in group order,
+ * one cast to out_dtype.  All strides are in elements and must be positive; c is row-major
+ * with row pitch ldc.  group_size in {32, 64, 128, 256}.
+ * Replaces the launch behind int8_gemm (src/grain_gemm/gemm.py:212-219): the Triton kernel
+ * src/grain_gemm/kernels/triton.py:54-63 and grain_cute_g256 (csrc/sm110/int8_g256_cute.cu:264).
+ * The tensor-core variants need A rows and B columns contiguous in K (a_sk == 1, b_sk == 1),
+ * 16-byte aligned bases and row pitches that are multiples of 16; anything else runs the
+ * CUDA-core variant (or fails with cudaErrorInvalidValue when a tensor-core variant was forced).
+ */
+int gg_int8_gemm(const void* a, const void* b, const void* scale_a, const void* scale_b, void* c,
+                 int m, int n, int k,
+                 long long a_sm, long long a_sk, long long b_sk, long long b_sn,
+                 long long sa_sm, long long sa_sg, long long sb_sg, long long sb_sn,
+                 long long ldc, int group_size, int out_dtype, int variant, void* stream);
+
+/* Variant gg_int8_gemm would run for these arguments (GG_VARIANT_*), without launching.
+ * Backs get_kernel_config (src/grain_gemm/gemm.py:84-178). */
+int gg_int8_gemm_select(const void* a, const void* b, const void* c, int m, int n, int k,
+                        long long a_sm, long long a_sk, long long b_sk, long long b_sn,
+                        long long ldc, int group_size, int out_dtype);
+
+/* Same GEMM on the CUDA-core kernel, additionally writing the INT32 group dots to
+ * partials[M, N, ceil(K/G)] (test aid for the "INT32 partials bit-exact" contract). */
+int gg_int8_gemm_partials(const void* a, const void* b, const void* scale_a, const void* scale_b,
+                          void* c_fp32, void* partials, int m, int n, int k,
+                          long long a_sm, long long a_sk, long long b_sk, long long b_sn,
+                          long long sa_sm, long long sa_sg, long long sb_sg, long long sb_sn,
+                          int group_size, void* stream);
+
+/* The reference's native GEMM entry point with its exact signature
+ * (csrc/sm110/int8_g256_cute.cu:264-266; ctypes declaration src/grain_gemm/kernels/cuda.py:85-88):
+ * G = 256, BF16 output, A [M,K] contiguous, B stored as Linear [N,K] contiguous, contiguous
+ * scales.  `config` is accepted and ignored (the library chooses the tile). */
+int grain_cute_g256(const void* a, const void* b, const void* scale_a, const void* scale_b,
+                    void* c, int m, int n, int k, int config, void* stream);
+const char* grain_cuda_error_string(int status);
+
+/* ---- MoE stages (src/grain_gemm/moe.py:253-346) ------------------------------------------ */
+
+/* Bytes of scratch gg_moe_route needs for T tokens, top-k R and E experts (may be 0). */
+size_t gg_moe_route_workspace_bytes(int tokens, int top_k, int experts);
+
+/*
+ * Routing metadata, replacing prepare_routes (src/grain_gemm/kernels/moe.py:222-291).
+ * ids: [T,R] int32 or int64 (ids_are_i64); mask: [T] bytes or NULL.
+ * effective_ids [T*R] (same width as ids), order [T*R] int64, inverse [T*R] int32,
+ * counts [E] int32, offsets [E+1] int32, statistics [3] int32 =
+ * (enabled ids outside [0,E), largest count, number of valid assignments).
+ */
+int gg_moe_route(const void* ids, int ids_are_i64, const void* mask, int tokens, int top_k,
+                 int experts, void* effective_ids, void* order, void* inverse, void* counts,
+                 void* offsets, void* statistics, void* workspace, size_t workspace_bytes,
+                 void* stream);
+
+/* Entries tile_expert / tile_row must hold for S assignments, E experts, tiles of tile_rows. */
+int gg_moe_tile_capacity(int assignments, int experts, int tile_rows);
+
+/* Cuts every expert's sorted rows into tiles of tile_rows rows; unused entries get expert -1.
+ * Replaces prepare_ragged_tiles (src/grain_gemm/kernels/moe.py:294-318). */
+int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, void* tile_expert,
+                 void* tile_row, void* stream);
+
+/*
+ * Gate/Up projection + rounding to out_dtype + SwiGLU + G256 requantisation over the sorted
+ * slots: q[S,I] int8 and s[S,I/256] fp32; rows are gathered from x[T,H] by order[slot] / R.
+ * w1: Linear [E,2I,H] contiguous int8; scale_w1: [E,H/256,2I] fp32.  interleaved != 0 means
+ * the 2I dimension is ordered [g0,u0,g1,u1,...].  tile_rows must be the value given to
+ * gg_moe_tiles: 128 selects the fused tensor-core kernel (needs 16-byte aligned x and w1),
+ * 32 the CUDA-core path, which needs gate_up_scratch[S,2I] of out_dtype.
+ * Replaces ragged_gemm + swiglu_quantize (src/grain_gemm/moe.py:298-304) and
+ * grain_moe_gather_launch / grain_moe_interleaved_launch
+ * (csrc/sm110/int8_g256_moe_gather.cu:380, int8_g256_moe_interleaved.cu:372).
+ */
+int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const void* scale_w1,
+                   const void* order, const void* offsets, const void* tile_expert,
+                   const void* tile_row, int tile_capacity, int tile_rows, void* q, void* s,
+                   void* gate_up_scratch, int tokens, int top_k, int experts, int hidden,
+                   int intermediate, int interleaved, int out_dtype, void* stream);
+
+/*
+ * Down projection over the sorted slots: expert_out[S,H] (out_dtype) from q[S,I], s[S,I/256],
+ * w2 Linear [E,H,I] contiguous int8, scale_w2 [E,I/256,H].  Rows at or beyond offsets[E] are
+ * not written.  tile_rows 128 = tensor cores, 32 = CUDA cores.
+ * Replaces the second ragged_gemm (src/grain_gemm/moe.py:305-308) and grain_cutlass_moe_g256
+ * (csrc/sm110/int8_g256_moe.cu:287).
+ */
+int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_w2,
+                const void* offsets, const void* tile_expert, const void* tile_row,
+                int tile_capacity, int tile_rows, void* expert_out, int assignments, int experts,
+                int hidden, int intermediate, int out_dtype, void* stream);
+
+/*
+ * out[T,H] = cast( sum_r float(expert_out[inverse[t*R+r]]) * weights[t,r] ), slots with
+ * inverse < 0 skipped, FP32 product and sum unfused.  Replaces combine
+ * (src/grain_gemm/kernels/moe.py:656-676).
+ */
+int gg_moe_combine(const void* expert_out, const void* weights, const void* inverse, void* out,
+                   int tokens, int top_k, int hidden, int out_dtype, void* stream);
+
+/*
+ * Reads (and clears) the device status word that kernels set when one of their bounded
+ * waits ran out.  Synchronises `stream`.  *status = 0 when every kernel completed normally.
+ */
+int gg_device_status(int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GRAIN_GEMM_B200_H */

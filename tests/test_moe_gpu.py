@@ -1,0 +1,259 @@
+"""Parity of the CUDA MoE stages (through the C ABI) with the CPU oracle and golden fixtures.
+
+Routing metadata and the INT8/INT32 parts are bit-exact.  The fused Gate/Up stage contains
+expf, which differs between CUDA and the host C library in the last bit, so quantised
+activations may move by one step on a rounding boundary: the stage test bounds that, and the
+Down and combine stages are checked bit-exactly on the CUDA path's own quantised activations.
+Final outputs: rtol 1e-3 / atol 1e-2 after BF16/FP16 rounding.
+"""
+
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import cpu as oracle
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-3, 1e-2
+
+
+@pytest.fixture(scope="module")
+def moe():
+    from grain_gemm_b200 import _loader, moe
+    assert _loader.is_available(), "libgrain_b200.so must be built for the GPU tests"
+    yield moe
+    assert _loader.device_status() == 0, "a kernel reported a bounded-wait timeout"
+
+
+def assert_routes_equal(routes, expected):
+    for field in ("order", "inverse", "counts", "offsets", "effective_ids", "statistics"):
+        actual = getattr(routes, field).cpu()
+        wanted = getattr(expected, field) if not isinstance(expected, dict) else expected[field]
+        assert actual.dtype == wanted.dtype, field
+        assert torch.equal(actual, wanted), field
+
+
+@pytest.mark.parametrize("name", ["mixed", "all_masked", "e32_t1031", "e64_t1031", "e65_t1031",
+                                  "e128_top8_int32"])
+def test_routes_match_reference_fixtures(moe, name):
+    case = load_golden(f"routes_{name}")
+    mask = case["mask"].bool().cuda() if "mask" in case else None
+    routes = moe.prepare_routes(case["ids"].cuda(), case["experts"], mask, tile_rows=0)
+    assert_routes_equal(routes, case)
+
+
+@pytest.mark.parametrize("tokens,top_k,experts,dtype", [
+    (0, 3, 5, torch.int64), (1, 1, 1, torch.int32), (128, 8, 128, torch.int32),
+    (1024, 1, 7, torch.int64), (1025, 1, 7, torch.int64), (512, 8, 128, torch.int64),
+    (16384, 8, 256, torch.int32), (4096, 2, 8, torch.int64), (3000, 5, 1000, torch.int32)])
+def test_routes_match_oracle(moe, tokens, top_k, experts, dtype):
+    gen = torch.Generator().manual_seed(tokens + experts)
+    ids = torch.randint(-2, experts + 2, (tokens, top_k), generator=gen).to(dtype)
+    mask = torch.rand((tokens,), generator=gen) > 0.1
+    for m in (None, mask):
+        expected = oracle.route(ids, experts, m)
+        routes = moe.prepare_routes(ids.cuda(), experts, m.cuda() if m is not None else None,
+                                    tile_rows=0)
+        assert_routes_equal(routes, expected)
+
+
+def test_tile_list(moe):
+    gen = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, 9, (700, 2), generator=gen)
+    for tile_rows in (32, 128):
+        routes = moe.prepare_routes(ids.cuda(), 9, None, tile_rows=tile_rows)
+        offsets = routes.offsets.cpu().tolist()
+        experts, rows = [], []
+        for e in range(9):
+            for start in range(offsets[e], offsets[e + 1], tile_rows):
+                experts.append(e)
+                rows.append(start)
+        used = len(experts)
+        assert routes.tile_expert.numel() == (1400 + tile_rows - 1) // tile_rows + 9
+        assert routes.tile_expert[:used].cpu().tolist() == experts
+        assert routes.tile_row[:used].cpu().tolist() == rows
+        assert (routes.tile_expert[used:] < 0).all()
+
+
+def make_case(tokens, hidden, inter, experts, top_k, *, seed=2026, layout="split",
+              dtype=torch.bfloat16, biased=False, mask=False, ids_dtype=torch.int64):
+    """Seeded synthetic MoE case with the value distributions of the BASELINE configurations."""
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randint(-127, 128, (tokens, hidden), dtype=torch.int8, generator=gen)
+    scale_x = (0.5 + torch.rand((tokens, hidden // 256), generator=gen)) / 127
+    logits = torch.randn((tokens, experts), generator=gen)
+    if biased:
+        logits[:, 0] += 2
+    weights, ids = torch.softmax(logits, dim=-1).topk(top_k, dim=-1)
+    weights = (weights / weights.sum(-1, keepdim=True)).float().contiguous()
+    w1 = torch.randint(-127, 128, (experts, 2 * inter, hidden), dtype=torch.int8, generator=gen)
+    w2 = torch.randint(-127, 128, (experts, hidden, inter), dtype=torch.int8, generator=gen)
+    w1[:, :, 0], w1[:, :, 1] = -128, 127
+    s1 = (0.5 + torch.rand((experts, hidden // 256, 2 * inter), generator=gen)) * (3 / hidden) ** 0.5 / 127
+    s2 = (0.5 + torch.rand((experts, inter // 256, hidden), generator=gen)) * (3 / inter) ** 0.5 / 127
+    s1[:, :, ::11] *= -1
+    s1[:, :, 5::17] = 0
+    if layout == "interleaved":
+        # Column order [g0, u0, g1, u1, ...] of the same logical weights.
+        permutation = torch.stack([torch.arange(inter), inter + torch.arange(inter)], 1).reshape(-1)
+        w1 = w1[:, permutation].contiguous()
+        s1 = s1[:, :, permutation].contiguous()
+    case = dict(hidden_states=x, w_gate_up=w1.transpose(-2, -1), w_down=w2.transpose(-2, -1),
+                topk_weights=weights, topk_ids=ids.to(ids_dtype).contiguous(), scale_x=scale_x,
+                scale_gate_up=s1, scale_down=s2, output_dtype=dtype, gate_up_layout=layout)
+    if mask:
+        case["token_mask"] = torch.rand((tokens,), generator=gen) > 0.2
+    return case
+
+
+def to_cuda(case):
+    return {k: v.cuda() if isinstance(v, torch.Tensor) else v for k, v in case.items()}
+
+
+def run_stages(moe, case, variant):
+    """Run the CUDA stages one by one and check each against the oracle on the same inputs."""
+    dev = to_cuda(case)
+    dtype, layout = case["output_dtype"], case["gate_up_layout"]
+    experts = case["w_gate_up"].shape[0]
+    tile_rows = 128 if variant == "tensor_core" else 32
+    mask = case.get("token_mask")
+    routes = moe.prepare_routes(dev["topk_ids"], experts, dev.get("token_mask"), tile_rows=tile_rows)
+    expected_routes = oracle.route(case["topk_ids"], experts, mask)
+    assert_routes_equal(routes, expected_routes)
+    valid = int(expected_routes.offsets[-1])
+
+    w1 = dev["w_gate_up"].transpose(-2, -1)
+    w2 = dev["w_down"].transpose(-2, -1)
+    qh, sh = moe.gate_up_swiglu_quantize(dev["hidden_states"], dev["scale_x"], w1,
+                                         dev["scale_gate_up"], routes, output_dtype=dtype,
+                                         gate_up_layout=layout)
+    gate_up = oracle.ragged_gemm(case["hidden_states"], case["w_gate_up"].transpose(-2, -1),
+                                 case["scale_x"], case["scale_gate_up"], expected_routes, dtype,
+                                 source_is_token=True)
+    expected_q, expected_s = oracle.swiglu_quantize(gate_up, valid, layout)
+    q_cpu, s_cpu = qh.cpu()[:valid], sh.cpu()[:valid]
+    torch.testing.assert_close(s_cpu, expected_s[:valid], rtol=2e-6, atol=0)
+    difference = (q_cpu.int() - expected_q[:valid].int()).abs()
+    assert difference.max() <= 1
+    assert (difference != 0).float().mean() < 2e-3
+
+    # Down and combine: bit-exact on the CUDA path's own quantised activations.
+    expert_out = moe.down_projection(qh, sh, w2, dev["scale_down"], routes, output_dtype=dtype)
+    expected_out = oracle.ragged_gemm(qh.cpu(), case["w_down"].transpose(-2, -1), sh.cpu(),
+                                      case["scale_down"], expected_routes, dtype,
+                                      source_is_token=False)
+    assert torch.equal(expert_out.cpu()[:valid], expected_out[:valid])
+    out = moe.combine(expert_out, dev["topk_weights"], routes, output_dtype=dtype)
+    expected_final = oracle.combine(expert_out.cpu(), case["topk_weights"], expected_routes, dtype)
+    assert torch.equal(out.cpu(), expected_final)
+    return out.cpu()
+
+
+SMALL_CASES = [
+    dict(tokens=7, hidden=512, inter=256, experts=5, top_k=3),
+    dict(tokens=129, hidden=512, inter=512, experts=4, top_k=4, mask=True),
+    dict(tokens=300, hidden=1024, inter=768, experts=16, top_k=2, layout="interleaved", biased=True),
+    dict(tokens=64, hidden=256, inter=256, experts=3, top_k=1, dtype=torch.float16,
+         ids_dtype=torch.int32),
+]
+
+
+@pytest.mark.parametrize("variant", ["cuda_core", "tensor_core"])
+@pytest.mark.parametrize("spec", SMALL_CASES, ids=lambda s: "-".join(f"{k}{v}" for k, v in s.items()))
+def test_stages_against_oracle(moe, spec, variant):
+    case = make_case(**spec)
+    staged = run_stages(moe, case, variant)
+    full = moe.moe_ffn(**to_cuda(case), variant=variant).cpu()
+    assert torch.equal(full, staged)
+    expected = oracle.moe_ffn(**{k: v for k, v in case.items()})
+    torch.testing.assert_close(full.float(), expected.float(), rtol=RTOL, atol=ATOL)
+    if "token_mask" in case:
+        assert full[~case["token_mask"]].abs().sum() == 0
+
+
+@pytest.mark.parametrize("label,dtype", [("bf16", torch.bfloat16), ("fp16", torch.float16)])
+@pytest.mark.parametrize("variant", ["cuda_core", "tensor_core"])
+def test_reference_fixture_case(moe, label, dtype, variant):
+    """The reference's own 7-token case (extrema weights, zero scales, repeated experts)."""
+    case = load_golden(f"moe_small_{label}")
+    tensors = dict(
+        hidden_states=case["hidden_states"],
+        w_gate_up=case["w_gate_up"].transpose(-2, -1).contiguous().transpose(-2, -1),
+        w_down=case["w_down"].transpose(-2, -1).contiguous().transpose(-2, -1),
+        topk_weights=case["topk_weights"], topk_ids=case["topk_ids"], scale_x=case["scale_x"],
+        scale_gate_up=case["scale_gate_up"], scale_down=case["scale_down"])
+    actual = moe.moe_ffn(**to_cuda(tensors), output_dtype=dtype, variant=variant).cpu()
+    # The reference's own tolerance for its FP64-approximated CPU check ...
+    torch.testing.assert_close(actual.float(), case["expected"], rtol=0.015, atol=0.025)
+    # ... and the tighter bar against the exact-fmaf oracle.
+    expected = oracle.moe_ffn(**tensors, output_dtype=dtype)
+    torch.testing.assert_close(actual.float(), expected.float(), rtol=RTOL, atol=ATOL)
+    mask = case["token_mask"].bool()
+    masked = moe.moe_ffn(**to_cuda(tensors), token_mask=mask.cuda(), output_dtype=dtype,
+                         variant=variant).cpu()
+    torch.testing.assert_close(masked.float(), case["expected_masked"], rtol=0.015, atol=0.025)
+    assert masked[~mask].abs().sum() == 0
+
+
+def test_masked_rows_may_hold_nan_and_out_of_range_ids(moe):
+    case = make_case(129, 512, 256, 4, 4, mask=True)
+    masked = ~case["token_mask"]
+    case["scale_x"][masked] = float("nan")
+    case["topk_weights"][masked] = float("nan")
+    case["topk_ids"][masked] = torch.tensor([2**40, -(2**40), 2**63 - 1, -(2**63)])
+    actual = moe.moe_ffn(**to_cuda(case)).cpu()
+    assert torch.isfinite(actual.float()).all()
+    assert actual[masked].abs().sum() == 0
+    expected = oracle.moe_ffn(**case)
+    torch.testing.assert_close(actual.float(), expected.float(), rtol=RTOL, atol=ATOL)
+
+
+def test_unmasked_invalid_ids_raise(moe):
+    case = make_case(8, 256, 256, 4, 2)
+    case["topk_ids"][3, 1] = 4
+    with pytest.raises(ValueError, match="topk_ids"):
+        moe.moe_ffn(**to_cuda(case))
+
+
+def test_interleaved_equals_split_bits(moe):
+    split = make_case(200, 512, 512, 6, 2, layout="split", seed=5)
+    inter = make_case(200, 512, 512, 6, 2, layout="interleaved", seed=5)
+    a = moe.moe_ffn(**to_cuda(split)).cpu()
+    b = moe.moe_ffn(**to_cuda(inter)).cpu()
+    assert torch.equal(a, b)
+
+
+def test_baseline_config_3_decode_small(moe):
+    """T=512, H=2048, I=768, E=128, top-8, split layout, BF16."""
+    case = make_case(512, 2048, 768, 128, 8)
+    actual = moe.moe_ffn(**to_cuda(case)).cpu()
+    expected = oracle.moe_ffn(**case)
+    torch.testing.assert_close(actual.float(), expected.float(), rtol=RTOL, atol=ATOL)
+
+
+def test_baseline_config_4_interleaved_decode(moe):
+    """H=4096, I=14336, E=8, top-2, T=16, one expert biased, interleaved layout."""
+    case = make_case(16, 4096, 14336, 8, 2, layout="interleaved", biased=True)
+    actual = moe.moe_ffn(**to_cuda(case)).cpu()
+    expected = oracle.moe_ffn(**case)
+    torch.testing.assert_close(actual.float(), expected.float(), rtol=RTOL, atol=ATOL)
+
+
+def test_graph_replay_with_changed_routes(moe):
+    case = to_cuda(make_case(64, 512, 256, 8, 2))
+    kwargs = {k: v for k, v in case.items()}
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            moe.moe_ffn(**kwargs)
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        captured = moe.moe_ffn(**kwargs)
+    graph.replay()
+    assert torch.equal(captured, moe.moe_ffn(**kwargs))
+    case["topk_ids"].copy_((case["topk_ids"] + 3) % 8)
+    graph.replay()
+    assert torch.equal(captured, moe.moe_ffn(**kwargs))
