@@ -562,4 +562,16 @@ int gg_device_status(int* status, void* stream_ptr) {
   return static_cast<int>(error);
 }
 
+#ifdef GG_TRACE
+// Debug builds only: copies the CTA-0 timeline to host memory (synchronises the device).
+int gg_debug_trace(long long* out, int entries) {
+  cudaError_t error = cudaDeviceSynchronize();
+  if (error != cudaSuccess) return static_cast<int>(error);
+  error = cudaMemcpyFromSymbol(out, gg::g_trace, sizeof(long long) * entries);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  static long long zeros[3 * 2048];
+  return static_cast<int>(cudaMemcpyToSymbol(gg::g_trace, zeros, sizeof(zeros)));
+}
+#endif
+
 }  // extern "C"

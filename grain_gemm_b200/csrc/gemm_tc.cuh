@@ -207,12 +207,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // Warps 8-11 (producer, MMA issuer, two spares) give registers to the promotion warps.
   if (warp >= 8) {
-  setmaxnreg_dec<56>();
+  setmaxnreg_dec<64>();
   if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t sequence = 0;
+      uint32_t stage = 0, phase = 0;
       bool ok = true;
+      [[maybe_unused]] int trace_cursor = 0;
       for (int tile = worker; tile < total_tiles && ok; tile += workers) {
         int tm, tn;
         tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
@@ -227,75 +228,92 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           row_a = (tm * kCtaGroup + static_cast<int>(cta_rank)) * Shape::kBM;
           row_b = tn * BN + static_cast<int>(cta_rank) * Shape::kBRows;
         }
-        for (int slab = 0; slab < slabs; ++slab, ++sequence) {
-          const uint32_t stage = sequence % kStages;
-          const uint32_t phase = (sequence / kStages) & 1u;
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, kSiteProducerEmpty, abort_flag)) {
+        for (int slab = 0, x = 0; slab < slabs; ++slab, x += Shape::kBK) {
+          if (!mbar_test(&empty_bar[stage], phase ^ 1u) &&
+              !mbar_wait(&empty_bar[stage], phase ^ 1u, kSiteProducerEmpty, abort_flag)) {
             ok = false;
             break;
           }
+          GG_TRACE_EVENT(0, trace_cursor, 1);
           uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
           uint8_t* b_dst = a_dst + Shape::kABytes;
           if constexpr (kCtaGroup == 1) {
             mbar_expect_tx(&full_bar[stage], Shape::kStageBytes);
-            tma_load_2d(a_dst, &map_a, &full_bar[stage], slab * Shape::kBK, row_a);
-            tma_load_2d(b_dst, &map_b, &full_bar[stage], slab * Shape::kBK, row_b);
+            tma_load_2d(a_dst, &map_a, &full_bar[stage], x, row_a);
+            tma_load_2d(b_dst, &map_b, &full_bar[stage], x, row_b);
           } else {
             if (cta_rank == 0) mbar_expect_tx(&full_bar[stage], 2 * Shape::kStageBytes);
-            tma_load_2d_pair(a_dst, &map_a, &full_bar[stage], slab * Shape::kBK, row_a);
-            tma_load_2d_pair(b_dst, &map_b, &full_bar[stage], slab * Shape::kBK, row_b);
+            tma_load_2d_pair(a_dst, &map_a, &full_bar[stage], x, row_a);
+            tma_load_2d_pair(b_dst, &map_b, &full_bar[stage], x, row_b);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
       }
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------ MMA issuer
+    // One thread issues every MMA; the loop body is kept to a handful of instructions per
+    // MMA (descriptor low words advance by constants, ring positions are running counters).
     if (cta_rank == 0 && lane == 0) {
       constexpr uint32_t idesc = make_idesc_i8(Shape::kBM * kCtaGroup, BN);
-      uint32_t sequence = 0;        // smem slabs consumed
-      uint32_t group_sequence = 0;  // accumulator buffers produced
+      const uint32_t a_low_base = smem_desc_low(smem_u32(stage_base));
+      uint32_t stage = 0, phase = 0;                 // shared-memory ring position
+      uint32_t buffer = 0, empty_parity = 1;         // TMEM ring position
+      int step = 0;                                  // MMAs issued into the open group
       bool ok = true;
+      [[maybe_unused]] int trace_cursor = 0;
       for (int tile = worker; tile < total_tiles && ok; tile += workers) {
         if constexpr (kGrouped) {
           int tm, tn;
           tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
           if (p.tile_expert[tm] < 0) continue;
         }
-        for (int kk = 0; kk < ksteps; ++kk) {
-          const int in_slab = kk & 3;
-          const uint32_t stage = sequence % kStages;
-          if (in_slab == 0) {
-            if (!mbar_wait(&full_bar[stage], (sequence / kStages) & 1u, kSiteMmaFull,
-                           abort_flag)) {
-              ok = false;
-              break;
+        int remaining = ksteps;
+        for (int slab = 0; slab < slabs && ok; ++slab) {
+          if (!mbar_test(&full_bar[stage], phase) &&
+              !mbar_wait(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          GG_TRACE_EVENT(1, trace_cursor, 1);
+          const uint32_t a_low = a_low_base + stage * (Shape::kStageBytes >> 4);
+          const uint32_t b_low = a_low + (Shape::kABytes >> 4);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (remaining > 0) {
+              if (step == 0) {
+                if (!mbar_test(&tmem_empty_bar[buffer], empty_parity) &&
+                    !mbar_wait(&tmem_empty_bar[buffer], empty_parity, kSiteMmaTmemEmpty,
+                               abort_flag)) {
+                  ok = false;
+                  break;
+                }
+                tcgen05_fence_after();
+                GG_TRACE_EVENT(1, trace_cursor, 2);
+              }
+              umma_i8<kCtaGroup>(tmem_base + buffer * BN, a_low + 2 * j, b_low + 2 * j, idesc,
+                                 step != 0 ? 1u : 0u);
+              ++step;
+              --remaining;
+              if (step == steps_per_group || remaining == 0) {
+                if constexpr (kCtaGroup == 1) umma_commit(&tmem_full_bar[buffer]);
+                else umma_commit_pair(&tmem_full_bar[buffer], 3);
+                GG_TRACE_EVENT(1, trace_cursor, 3);
+                step = 0;
+                buffer ^= 1u;
+                if (buffer == 0) empty_parity ^= 1u;
+              }
             }
-            tcgen05_fence_after();
           }
-          const int in_group = kk % steps_per_group;
-          const uint32_t buffer = group_sequence & 1u;
-          if (in_group == 0) {
-            if (!mbar_wait(&tmem_empty_bar[buffer], ((group_sequence >> 1) & 1u) ^ 1u,
-                           kSiteMmaTmemEmpty, abort_flag)) {
-              ok = false;
-              break;
-            }
-            tcgen05_fence_after();
-          }
-          const uint32_t a_addr = smem_u32(stage_base + stage * Shape::kStageBytes) + in_slab * 32;
-          const uint32_t b_addr = a_addr + Shape::kABytes;
-          umma_i8<kCtaGroup>(tmem_base + buffer * BN, make_smem_desc_sw128(a_addr),
-                             make_smem_desc_sw128(b_addr), idesc, in_group != 0 ? 1u : 0u);
-          const bool last_step = kk == ksteps - 1;
-          if (in_group == steps_per_group - 1 || last_step) {
-            if constexpr (kCtaGroup == 1) umma_commit(&tmem_full_bar[buffer]);
-            else umma_commit_pair(&tmem_full_bar[buffer], 3);
-            ++group_sequence;
-          }
-          if (in_slab == 3 || last_step) {
-            if constexpr (kCtaGroup == 1) umma_commit(&empty_bar[stage]);
-            else umma_commit_pair(&empty_bar[stage], 3);
-            ++sequence;
+          if constexpr (kCtaGroup == 1) umma_commit(&empty_bar[stage]);
+          else umma_commit_pair(&empty_bar[stage], 3);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
       }
@@ -311,6 +329,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int col_base = half * kNC;
     uint32_t group_sequence = 0;
     bool ok = true;
+    [[maybe_unused]] int trace_cursor = 0;
     OutT* c = reinterpret_cast<OutT*>(p.c);
     // A failed wait clears `ok` but the loops keep their shape, so that every thread still
     // reaches every named barrier the others wait on.
@@ -356,16 +375,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           ok = false;
         }
         tcgen05_fence_after();
+        if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 1);
         const float* sb_slot = sb_ring + (g & 1) * BN + col_base;
         const uint32_t taddr =
             tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN + col_base;
+        // Two register buffers: the load of chunk c+1 is in flight while chunk c is promoted.
+        uint32_t partial_a[32], partial_b[32];
+        if (ok) tmem_ld_32x32b_x32(taddr, partial_a);
 #pragma unroll
         for (int chunk = 0; chunk < kNC / 32; ++chunk) {
           if (!ok) break;
-          uint32_t partial[32];
-          tmem_ld_32x32b_x32(taddr + chunk * 32, partial);
           tmem_ld_wait();
-          if (chunk == kNC / 32 - 1) {
+          if (chunk + 1 < kNC / 32) {
+            if (chunk & 1) tmem_ld_32x32b_x32(taddr + (chunk + 1) * 32, partial_a);
+            else tmem_ld_32x32b_x32(taddr + (chunk + 1) * 32, partial_b);
+          } else {
             // All of this warp's TMEM reads for the buffer are done: hand it back.
             tcgen05_fence_before();
             __syncwarp();
@@ -374,10 +398,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               else mbar_arrive_cluster(&tmem_empty_bar[buffer], 0);
             }
           }
-          promote32(partial, sa, sb_slot + chunk * 32, acc + chunk * 32);
+          if (chunk & 1) promote32(partial_b, sa, sb_slot + chunk * 32, acc + chunk * 32);
+          else promote32(partial_a, sa, sb_slot + chunk * 32, acc + chunk * 32);
         }
+        if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 2);
         if (tid < BN) sb_ring[((g + 1) & 1) * BN + tid] = sb_next;
         named_barrier_sync(1, 256);
+        if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 3);
       }
       if (row_ok && ok) {
         OutT* c_row = c + static_cast<long long>(row) * p.ldc + n0 + col_base;

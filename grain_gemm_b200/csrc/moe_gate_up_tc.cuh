@@ -13,7 +13,8 @@
 //
 // Work item = (128-row tile of one expert, 256-channel group), processed as two sub-tiles of
 // 128 channels; a sub-tile is one N = 256 accumulator (128 gate + 128 up columns) in TMEM.
-//   warp 8    producer: TMA for the two weight boxes, 16-byte cp.async gather for x rows
+//   warps 8, 10, 11   producers: 16-byte cp.async gather of the x rows (96 threads); lane 0 of
+//             warp 8 also issues the TMA loads of the two weight boxes
 //   warp 9    MMA issuer (tcgen05.mma kind::i8, two TMEM buffers)
 //   warps 0-7 promotion per K group, then SwiGLU; the first sub-tile's h is parked in shared
 //             memory until the second sub-tile supplies the other half of the row maximum.
@@ -103,11 +104,10 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
   const int total_items = p.max_tiles * channel_groups;
   const int groups = p.hidden / 256;
   const int slabs = p.hidden / 128;
-  const int ksteps = p.hidden / 32;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(&full_bar[i], 33);  // 32 gather lanes + the TMA transaction arrival
+      mbar_init(&full_bar[i], 97);  // 96 gather threads + the TMA transaction arrival
       mbar_init(&empty_bar[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -126,10 +126,15 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
 
   // Warps 8-11 (producer, MMA issuer, two spares) give registers to the promotion warps.
   if (warp >= 8) {
-  setmaxnreg_dec<56>();
-  if (warp == 8) {
-    // ------------------------------------------------------------ producer
-    uint32_t sequence = 0;
+  setmaxnreg_dec<64>();
+  if (warp != 9) {
+    // ------------------------------------------------------------ producers (warps 8, 10, 11)
+    // 96 gather threads: thread g copies 16-byte chunk (g & 7) of rows (g >> 3) + 12 * i.
+    // Lane 0 of warp 8 also issues the TMA loads of the two weight boxes.
+    const int gather_id = (warp == 8 ? 0 : warp - 9) * 32 + lane;
+    const int chunk = gather_id & 7;
+    const int row_group = gather_id >> 3;
+    uint32_t stage = 0, phase = 0, issued = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
       const int tile = item / channel_groups;
@@ -138,50 +143,58 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
       if (expert < 0) continue;
       const int row0 = p.tile_row[tile];
       const int row_end = p.expert_offsets[expert + 1];
-      __syncwarp();
+      const int8_t* source[11];
+      uint32_t valid_mask = 0;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = lane + 32 * i;
+      for (int i = 0; i < 11; ++i) {
+        const int r = row_group + 12 * i;
         const int row = row0 + r;
-        tile_tokens[r] = row < row_end ? static_cast<int>(p.order[row] / p.top_k) : -1;
+        const bool valid = r < 128 && row < row_end;
+        const long long token = valid ? p.order[row] / p.top_k : 0;
+        source[i] = p.x + token * p.hidden + chunk * 16;
+        valid_mask |= valid ? (1u << i) : 0u;
       }
-      __syncwarp();
       for (int sub = 0; sub < 2 && ok; ++sub) {
         const int channel0 = jg * 256 + sub * 128;
         const int w_base = expert * 2 * p.intermediate;
         const int row_gate = p.interleaved ? w_base + 2 * channel0 : w_base + channel0;
         const int row_up = p.interleaved ? row_gate + 128 : w_base + p.intermediate + channel0;
-        for (int slab = 0; slab < slabs; ++slab, ++sequence) {
-          const uint32_t stage = sequence % kStages;
-          // All 32 lanes wait; the vote keeps the warp's control flow uniform on failure.
-          const bool got = mbar_wait(&empty_bar[stage], ((sequence / kStages) & 1u) ^ 1u,
-                                     kSiteProducerEmpty, abort_flag);
+        for (int slab = 0, x = 0; slab < slabs; ++slab, x += 128) {
+          // Every lane waits; the vote keeps the warp's control flow uniform on failure.
+          const bool got = mbar_test(&empty_bar[stage], phase ^ 1u) ||
+                           mbar_wait(&empty_bar[stage], phase ^ 1u, kSiteProducerEmpty, abort_flag);
           if (!__all_sync(0xffffffffu, got)) {
             ok = false;
             break;
           }
           uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
-          uint8_t* b_dst = a_dst + Shape::kABytes;
-          if (lane == 0) {
+          if (warp == 8 && lane == 0) {
+            uint8_t* b_dst = a_dst + Shape::kABytes;
             mbar_expect_tx(&full_bar[stage], Shape::kBBytes);
-            tma_load_2d(b_dst, &map_w, &full_bar[stage], slab * 128, row_gate);
-            tma_load_2d(b_dst + 128 * 128, &map_w, &full_bar[stage], slab * 128, row_up);
+            tma_load_2d(b_dst, &map_w, &full_bar[stage], x, row_gate);
+            tma_load_2d(b_dst + 128 * 128, &map_w, &full_bar[stage], x, row_up);
           }
           const uint32_t a_smem = smem_u32(a_dst);
-          const int chunk = lane & 7;
-#pragma unroll 8
-          for (int i = 0; i < 32; ++i) {
-            const int r = (lane >> 3) + 4 * i;
-            const int token = tile_tokens[r];
-            const int8_t* src = p.x + (token >= 0 ? static_cast<long long>(token) * p.hidden : 0) +
-                                slab * 128 + chunk * 16;
-            cp_async_16_zfill(a_smem + r * 128 + ((chunk ^ (r & 7)) << 4), src, token >= 0);
+#pragma unroll
+          for (int i = 0; i < 11; ++i) {
+            const int r = row_group + 12 * i;
+            if (r < 128) {
+              cp_async_16_zfill(a_smem + r * 128 + ((chunk ^ (r & 7)) << 4), source[i] + x,
+                                (valid_mask >> i) & 1u);
+            }
           }
           cp_async_commit();
-          if (sequence >= Shape::kGatherLag) {
+          ++issued;
+          if (issued > Shape::kGatherLag) {
+            // The slab issued kGatherLag iterations ago has landed: publish it.
             cp_async_wait<Shape::kGatherLag>();
             fence_proxy_async();
-            mbar_arrive(&full_bar[(sequence - Shape::kGatherLag) % kStages]);
+            const uint32_t done_stage = (stage + kStages - Shape::kGatherLag) % kStages;
+            mbar_arrive(&full_bar[done_stage]);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
       }
@@ -190,51 +203,56 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
     cp_async_wait<0>();
     fence_proxy_async();
     if (ok) {
-      const uint32_t first = sequence >= Shape::kGatherLag ? sequence - Shape::kGatherLag : 0;
-      for (uint32_t q = first; q < sequence; ++q) mbar_arrive(&full_bar[q % kStages]);
+      const uint32_t pending = issued < Shape::kGatherLag ? issued : Shape::kGatherLag;
+      for (uint32_t back = pending; back >= 1; --back) {
+        mbar_arrive(&full_bar[(stage + kStages * 2 - back) % kStages]);
+      }
     }
-  } else if (warp == 9) {
+  } else {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_i8(128, BN);
-      uint32_t sequence = 0, group_sequence = 0;
+      const uint32_t a_low_base = smem_desc_low(smem_u32(stage_base));
+      uint32_t stage = 0, phase = 0;
+      uint32_t buffer = 0, empty_parity = 1;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         const int tile = item / channel_groups;
         if (p.tile_expert[tile] < 0) continue;
         for (int sub = 0; sub < 2 && ok; ++sub) {
-          for (int kk = 0; kk < ksteps; ++kk) {
-            const int in_slab = kk & 3;
-            const uint32_t stage = sequence % kStages;
-            if (in_slab == 0) {
-              if (!mbar_wait(&full_bar[stage], (sequence / kStages) & 1u, kSiteMmaFull,
+          for (int slab = 0; slab < slabs && ok; ++slab) {
+            if (!mbar_test(&full_bar[stage], phase) &&
+                !mbar_wait(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after();
+            const bool group_start = (slab & 1) == 0;
+            if (group_start) {
+              if (!mbar_test(&tmem_empty_bar[buffer], empty_parity) &&
+                  !mbar_wait(&tmem_empty_bar[buffer], empty_parity, kSiteMmaTmemEmpty,
                              abort_flag)) {
                 ok = false;
                 break;
               }
               tcgen05_fence_after();
             }
-            const int in_group = kk & 7;
-            const uint32_t buffer = group_sequence & 1u;
-            if (in_group == 0) {
-              if (!mbar_wait(&tmem_empty_bar[buffer], ((group_sequence >> 1) & 1u) ^ 1u,
-                             kSiteMmaTmemEmpty, abort_flag)) {
-                ok = false;
-                break;
-              }
-              tcgen05_fence_after();
+            const uint32_t a_low = a_low_base + stage * (Shape::kStageBytes >> 4);
+            const uint32_t b_low = a_low + (Shape::kABytes >> 4);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              umma_i8<1>(tmem_base + buffer * BN, a_low + 2 * j, b_low + 2 * j, idesc,
+                         (group_start && j == 0) ? 0u : 1u);
             }
-            const uint32_t a_addr = smem_u32(stage_base + stage * Shape::kStageBytes) + in_slab * 32;
-            const uint32_t b_addr = a_addr + Shape::kABytes;
-            umma_i8<1>(tmem_base + buffer * BN, make_smem_desc_sw128(a_addr),
-                       make_smem_desc_sw128(b_addr), idesc, in_group != 0 ? 1u : 0u);
-            if (in_group == 7) {
+            umma_commit(&empty_bar[stage]);
+            if (!group_start) {
               umma_commit(&tmem_full_bar[buffer]);
-              ++group_sequence;
+              buffer ^= 1u;
+              if (buffer == 0) empty_parity ^= 1u;
             }
-            if (in_slab == 3) {
-              umma_commit(&empty_bar[stage]);
-              ++sequence;
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
             }
           }
         }
@@ -291,21 +309,28 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
           tcgen05_fence_after();
           const float* sb_slot = sb_ring + (g & 1) * BN;
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN;
-#pragma unroll
-          for (int chunk = 0; chunk < 4; ++chunk) {
-            if (!ok) break;
-            // Split layout: chunks 0,1 are this thread's gate columns, 2,3 its up columns.
-            const int column = p.interleaved ? half * 128 + chunk * 32
-                                             : (chunk >> 1) * 128 + half * 64 + (chunk & 1) * 32;
-            uint32_t partial[32];
-            tmem_ld_32x32b_x32(taddr + column, partial);
+          // Split layout: chunks 0,1 are this thread's gate columns, 2,3 its up columns.
+          const int column0 = p.interleaved ? half * 128 : half * 64;
+          const int column1 = column0 + 32;
+          const int column2 = p.interleaved ? half * 128 + 64 : 128 + half * 64;
+          const int column3 = column2 + 32;
+          uint32_t partial_a[32], partial_b[32];
+          if (ok) {
+            tmem_ld_32x32b_x32(taddr + column0, partial_a);
             tmem_ld_wait();
-            if (chunk == 3) {
-              tcgen05_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
-            }
-            promote32(partial, sa, sb_slot + column, acc + chunk * 32);
+            tmem_ld_32x32b_x32(taddr + column1, partial_b);
+            promote32(partial_a, sa, sb_slot + column0, acc);
+            tmem_ld_wait();
+            tmem_ld_32x32b_x32(taddr + column2, partial_a);
+            promote32(partial_b, sa, sb_slot + column1, acc + 32);
+            tmem_ld_wait();
+            tmem_ld_32x32b_x32(taddr + column3, partial_b);
+            promote32(partial_a, sa, sb_slot + column2, acc + 64);
+            tmem_ld_wait();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
+            promote32(partial_b, sa, sb_slot + column3, acc + 96);
           }
           sb_ring[((g + 1) & 1) * BN + tid] = sb_next;
           named_barrier_sync(1, 256);

@@ -28,6 +28,20 @@ __device__ __forceinline__ void report_timeout(unsigned int site) {
   atomicAdd(&g_device_status[1], 1u);
 }
 
+// Optional timeline of CTA 0 (build with -DGG_TRACE): per role a list of (tag, SM clock).
+#ifdef GG_TRACE
+__device__ long long g_trace[3 * 2048];
+__device__ __forceinline__ void trace_event(int role, int& cursor, int tag) {
+  if (blockIdx.x == 0 && cursor < 2048) {
+    g_trace[role * 2048 + cursor] = (static_cast<long long>(tag) << 56) | (clock64() & 0xffffffffffffffll);
+    ++cursor;
+  }
+}
+#define GG_TRACE_EVENT(role, cursor, tag) trace_event(role, cursor, tag)
+#else
+#define GG_TRACE_EVENT(role, cursor, tag)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -95,6 +109,21 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                "r"(bytes)
                : "memory");
+}
+
+// Single non-blocking probe of a phase parity.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
 }
 
 // Bounded wait on a phase parity.  Returns false (after reporting `site`) when the
@@ -218,26 +247,40 @@ __host__ __device__ constexpr uint32_t make_idesc_i8(int m, int n) {
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// High word of the shared-memory descriptor above (stride byte offset 1024, version 1,
+// SWIZZLE_128B) and its low word for a given shared address; the issuing loop keeps the low
+// word in a register and adds 2 per 32 bytes of K.
+constexpr uint32_t kSmemDescHighSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_low(uint32_t smem_addr) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+}
+
 template <int kCtaGroup>
-__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint32_t desc_a_low, uint32_t desc_b_low,
                                         uint32_t idesc, uint32_t accumulate) {
   if constexpr (kCtaGroup == 1) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t"
         "}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        "r"(desc_a_low), "r"(desc_b_low), "r"(idesc), "r"(accumulate), "r"(kSmemDescHighSw128)
         : "memory");
   } else {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, p;\n\t"
         "}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        "r"(desc_a_low), "r"(desc_b_low), "r"(idesc), "r"(accumulate), "r"(kSmemDescHighSw128)
         : "memory");
   }
 }
