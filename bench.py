@@ -1,0 +1,315 @@
+"""Benchmark of the hot paths: prints ONE JSON line (rank 0).
+
+Headline workload (N = 1): the W8A8 G256 GEMM at M = N = K = 8192 with BF16 output
+(seeded synthetic INT8 operands uniform in [-127, 127], lognormal FP32 scales), metric
+``g256_gemm_effective_int8_tops`` = 2*M*N*K / t.  A step is one GEMM over inputs resident in
+HBM.  ``e2e`` is the same metric through the public ``int8_gemm`` call with HOST (pinned)
+operands: host-to-device copies of A, B and the scales and the device-to-host read of C are
+inside the timed region.
+
+N > 1 (``torchrun``): the GEMM is sharded along N with no data-path collective (every rank
+owns its own 8192-column block of B and of C; A and scale_a are replicated), weak scaling;
+the MoE FFN (``--workload moe``) is expert-parallel with NCCL all-to-all.
+
+``--impl reference`` times the reference's CPU path for the same metric: the CPU oracle
+(``oracle/``, a restatement of the reference's arithmetic; the reference ships no compiled
+CPU implementation) on a bounded row sample of the same workload, all host threads.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# DRAM traffic of one launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum
+# from the ncu capture summarised in profiles/); None until a capture exists for the workload.
+NCU_TRAFFIC_BYTES = {"gemm_g256_m8192_n8192_k8192_bf16": None}
+
+
+def parse():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default="gemm", choices=["gemm", "moe"])
+    parser.add_argument("--m", type=int, default=8192)
+    parser.add_argument("--n", type=int, default=8192)
+    parser.add_argument("--k", type=int, default=8192)
+    parser.add_argument("--group-size", type=int, default=256)
+    parser.add_argument("--variant", default="auto")
+    parser.add_argument("--skip-cpu-baseline", action="store_true")
+    parser.add_argument("--skip-e2e", action="store_true")
+    return parser.parse_args()
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return dict(hbm_gbs=data["hbm_gbs"], bf16_tflops=data["bf16_tflops"],
+                    bf16_tflops_sustained=data.get("bf16_tflops_sustained"), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.device_index = device_index
+        self.process = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.device_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.process is not None:
+            time.sleep(0.15)
+            self.process.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) < 9:
+                continue
+            try:
+                clocks.append(float(fields[1]))
+                maxima.append(float(fields[2]))
+            except ValueError:
+                continue
+            for name, value in zip(names, fields[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": max(maxima),
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def make_gemm_inputs(m, n, k, group, seed, device, weight_seed=None):
+    """A [m,k] and scale_a from `seed`; Linear-format weights [n,k] and scale_b from
+    `weight_seed` (so that ranks can share A and own different column blocks of B)."""
+    groups = (k + group - 1) // group
+    generator = torch.Generator(device=device).manual_seed(seed)
+    a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=device, generator=generator)
+    scale_a = torch.exp(-5 + 0.5 * torch.randn((m, groups), device=device, generator=generator))
+    generator = torch.Generator(device=device).manual_seed(seed + 1 if weight_seed is None else weight_seed)
+    w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=device, generator=generator)
+    scale_b = torch.exp(-5 + 0.5 * torch.randn((groups, n), device=device, generator=generator))
+    return a, w, scale_a, scale_b
+
+
+def gemm_bytes(m, n, k, group, out_bytes=2):
+    groups = (k + group - 1) // group
+    return m * k + n * k + 4 * m * groups + 4 * groups * n + out_bytes * m * n
+
+
+def cpu_gemm_sample(m, n, k, group, budget_seconds=10.0):
+    """Times the CPU oracle on a row sample of the workload sized for about `budget_seconds`
+    of work; returns (TOPS, seconds, rows, threads)."""
+    from oracle import cpu as oracle
+    probe_rows = 8
+    a, w, scale_a, scale_b = make_gemm_inputs(min(m, 4096), n, k, group, 2026, "cpu")
+    b = w.t()
+    start = time.perf_counter()
+    oracle.int8_gemm(a[:probe_rows], b, scale_a[:probe_rows], scale_b, group, torch.bfloat16)
+    probe = time.perf_counter() - start
+    rows = int(max(probe_rows, min(a.shape[0], budget_seconds / max(probe, 1e-6) * probe_rows)))
+    start = time.perf_counter()
+    oracle.int8_gemm(a[:rows], b, scale_a[:rows], scale_b, group, torch.bfloat16)
+    elapsed = time.perf_counter() - start
+    return 2.0 * rows * n * k / elapsed / 1e12, elapsed, rows, oracle.threads()
+
+
+def run_reference_arm(args, rank):
+    """The reference's CPU path (oracle port) on a bounded sample, rank 0 only."""
+    if rank != 0:
+        return
+    m, n, k, g = args.m, args.n, args.k, args.group_size
+    samples = []
+    for _ in range(max(1, min(args.steps, 3))):
+        samples.append(cpu_gemm_sample(m, n, k, g, budget_seconds=8.0))
+    samples.sort(key=lambda item: item[0])
+    value, seconds, rows, threads = samples[len(samples) // 2]
+    times = samples
+    sample = f"{rows} rows of A against the full B (N={n}, K={k}); TOPS = 2*rows*N*K/t"
+    line = {
+        "impl": "reference", "metric": "g256_gemm_effective_int8_tops", "value": value,
+        "unit": "TOPS", "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
+        "ms_per_step": seconds * 1e3 * (m / rows), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": f"gemm_g{g}_m{m}_n{n}_k{k}_bf16", "sampled_rows": rows},
+        "cpu_baseline": {"value": value, "unit": "TOPS", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if args.workload == "moe":
+        from grain_gemm_b200 import bench_moe
+        bench_moe.run(args, rank, world, local_rank)
+        return
+
+    import torch.distributed as dist
+    from grain_gemm_b200 import _loader, gemm
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    m, n, k, g = args.m, args.n, args.k, args.group_size
+    # Rank r owns columns [r*n, (r+1)*n) of B, scale_b and C; A and scale_a are replicated.
+    a, w, scale_a, scale_b = make_gemm_inputs(m, n, k, g, 2026, device, weight_seed=3000 + rank)
+    b = w.t()
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+    workload = f"gemm_g{g}_m{m}_n{n * world}_k{k}_bf16"
+
+    def step():
+        gemm.launch(a, b, scale_a, scale_b, out, g, args.variant)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as sampler:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            step()
+        stop.record()
+        barrier()
+    elapsed_ms = start.elapsed_time(stop)
+    if world > 1:
+        reduced = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(reduced, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(reduced.item())
+    ms_per_step = elapsed_ms / args.steps
+    status = _loader.device_status(device)
+    if status:
+        raise SystemExit(f"a kernel reported device status {status:#x}")
+    tops = 2.0 * m * n * world * k / (ms_per_step * 1e-3) / 1e12
+
+    # End to end through the public API with host operands.
+    e2e = None
+    if not args.skip_e2e:
+        host = [t.cpu().pin_memory() for t in (a, w, scale_a, scale_b)]
+        host_out = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+        h2d = sum(t.numel() * t.element_size() for t in host)
+        d2h = host_out.numel() * host_out.element_size()
+
+        def e2e_step():
+            da, dw, dsa, dsb = (t.to(device, non_blocking=True) for t in host)
+            result = gemm.int8_gemm(da, dw.t(), dsa, dsb, group_size=g, output_dtype=torch.bfloat16)
+            host_out.copy_(result, non_blocking=True)
+
+        e2e_steps = max(2, min(args.steps, 5))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        start.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        stop.record()
+        barrier()
+        e2e_ms = start.elapsed_time(stop)
+        if world > 1:
+            reduced = torch.tensor([e2e_ms], device=device)
+            dist.all_reduce(reduced, op=dist.ReduceOp.MAX)
+            e2e_ms = float(reduced.item())
+        e2e_ms /= e2e_steps
+        e2e = {"value": 2.0 * m * n * world * k / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    per_gpu_tops = tops / world
+    roofline = {
+        "bound": "tensor", "achieved": per_gpu_tops, "peak": int8_peak, "unit": "TFLOP/s",
+        "frac": per_gpu_tops / int8_peak,
+        "traffic": NCU_TRAFFIC_BYTES.get(f"gemm_g{g}_m{m}_n{n}_k{k}_bf16"),
+        "peak_source": f"2 x bf16_tflops burst ({peaks['source']}); MEASURED_PEAKS has no INT8 entry",
+        "frac_of_nominal_4500": per_gpu_tops / 4500.0,
+        "algorithmic_ops_per_launch": 2.0 * m * n * k,
+        "algorithmic_bytes_per_launch": gemm_bytes(m, n, k, g),
+        "kernel": gemm.get_kernel_config(a, b, group_size=g)["variant"],
+    }
+    line = {
+        "metric": "g256_gemm_effective_int8_tops", "value": tops, "unit": "TOPS", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic",
+        "config": {"workload": workload, "group_size": g, "output": "bf16",
+                   "sharding": "replicas" if world == 1 else f"n_sharded_x{world}",
+                   "l2": "inputs_larger_than_l2 (A + B + C = 256 MiB per GPU, no flush)"},
+        "roofline": roofline, "clocks": sampler.summary(), "gpu_launches": args.steps,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    if world == 1 and not args.skip_cpu_baseline:
+        cpu_tops, seconds, rows, threads = cpu_gemm_sample(m, n, k, g)
+        line["cpu_baseline"] = {
+            "value": cpu_tops, "unit": "TOPS", "cores": threads, "kind": "port",
+            "sample": f"{rows} rows of A against the full B ({seconds:.2f} s); scaled by rows"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

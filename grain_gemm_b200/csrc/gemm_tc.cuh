@@ -129,24 +129,43 @@ __device__ __forceinline__ void store_row_vector8(OutT* dst, const float* v) {
   }
 }
 
-// One promotion step over 32 drained columns: acc = fmaf(float(partial), sa*sb, acc).
+// One promotion step over 32 drained columns: acc = fmaf(float(partial), sa*sb, acc), two
+// columns per packed FP32 instruction (IEEE round-to-nearest per lane, bit-identical to the
+// scalar mul.rn / fma.rn).  GG_SCALAR_PROMOTE selects the scalar form for comparison.
 __device__ __forceinline__ void promote32(const uint32_t (&partial)[32], float sa,
-                                          const float* __restrict__ sb_smem, float* acc) {
+                                          const float* __restrict__ sb_smem, float2* acc) {
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
     const float4 sb = *reinterpret_cast<const float4*>(sb_smem + j);
-    const float2 s01 = mul2(make_float2(sa, sa), make_float2(sb.x, sb.y));
-    const float2 s23 = mul2(make_float2(sa, sa), make_float2(sb.z, sb.w));
+#ifdef GG_CONVERT_I2F
     const float2 p01 = make_float2(__int2float_rn(static_cast<int>(partial[j + 0])),
                                    __int2float_rn(static_cast<int>(partial[j + 1])));
     const float2 p23 = make_float2(__int2float_rn(static_cast<int>(partial[j + 2])),
                                    __int2float_rn(static_cast<int>(partial[j + 3])));
-    const float2 r01 = fma2(p01, s01, make_float2(acc[j + 0], acc[j + 1]));
-    const float2 r23 = fma2(p23, s23, make_float2(acc[j + 2], acc[j + 3]));
-    acc[j + 0] = r01.x;
-    acc[j + 1] = r01.y;
-    acc[j + 2] = r23.x;
-    acc[j + 3] = r23.y;
+#else
+    // Exact INT32 -> FP32 for |partial| <= 2^22 (a 256-long dot of INT8 products) without the
+    // conversion unit: the integer is added to the bit pattern of 1.5 * 2^23, whose unit in
+    // the last place is 1, then 1.5 * 2^23 is subtracted again; both steps are exact.
+    const float2 bias = make_float2(-12582912.0f, -12582912.0f);
+    const float2 p01 = __fadd2_rn(
+        make_float2(__uint_as_float(partial[j + 0] + 0x4B400000u),
+                    __uint_as_float(partial[j + 1] + 0x4B400000u)), bias);
+    const float2 p23 = __fadd2_rn(
+        make_float2(__uint_as_float(partial[j + 2] + 0x4B400000u),
+                    __uint_as_float(partial[j + 3] + 0x4B400000u)), bias);
+#endif
+#ifdef GG_SCALAR_PROMOTE
+    acc[j / 2].x = __fmaf_rn(p01.x, __fmul_rn(sa, sb.x), acc[j / 2].x);
+    acc[j / 2].y = __fmaf_rn(p01.y, __fmul_rn(sa, sb.y), acc[j / 2].y);
+    acc[j / 2 + 1].x = __fmaf_rn(p23.x, __fmul_rn(sa, sb.z), acc[j / 2 + 1].x);
+    acc[j / 2 + 1].y = __fmaf_rn(p23.y, __fmul_rn(sa, sb.w), acc[j / 2 + 1].y);
+#else
+    const float2 sa2 = make_float2(sa, sa);
+    const float2 s01 = __fmul2_rn(sa2, make_float2(sb.x, sb.y));
+    const float2 s23 = __fmul2_rn(sa2, make_float2(sb.z, sb.w));
+    acc[j / 2] = __ffma2_rn(p01, s01, acc[j / 2]);
+    acc[j / 2 + 1] = __ffma2_rn(p23, s23, acc[j / 2 + 1]);
+#endif
   }
 }
 
@@ -271,6 +290,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
           if (p.tile_expert[tm] < 0) continue;
         }
+        if (steps_per_group == 8 && (p.k & 255) == 0) {
+          // G = 256 with whole groups: two slabs per group, no per-MMA bookkeeping.
+          for (int slab = 0; slab < slabs && ok; ++slab) {
+            if (!mbar_test(&full_bar[stage], phase) &&
+                !mbar_wait(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after();
+            GG_TRACE_EVENT(1, trace_cursor, 1);
+            const bool group_start = (slab & 1) == 0;
+            if (group_start) {
+              if (!mbar_test(&tmem_empty_bar[buffer], empty_parity) &&
+                  !mbar_wait(&tmem_empty_bar[buffer], empty_parity, kSiteMmaTmemEmpty,
+                             abort_flag)) {
+                ok = false;
+                break;
+              }
+              tcgen05_fence_after();
+              GG_TRACE_EVENT(1, trace_cursor, 2);
+            }
+            const uint32_t a_low = a_low_base + stage * (Shape::kStageBytes >> 4);
+            const uint32_t b_low = a_low + (Shape::kABytes >> 4);
+            const uint32_t tmem_d = tmem_base + buffer * BN;
+            umma_i8<kCtaGroup>(tmem_d, a_low, b_low, idesc, group_start ? 0u : 1u);
+            umma_i8<kCtaGroup>(tmem_d, a_low + 2, b_low + 2, idesc, 1u);
+            umma_i8<kCtaGroup>(tmem_d, a_low + 4, b_low + 4, idesc, 1u);
+            umma_i8<kCtaGroup>(tmem_d, a_low + 6, b_low + 6, idesc, 1u);
+            if constexpr (kCtaGroup == 1) umma_commit(&empty_bar[stage]);
+            else umma_commit_pair(&empty_bar[stage], 3);
+            if (!group_start) {
+              if constexpr (kCtaGroup == 1) umma_commit(&tmem_full_bar[buffer]);
+              else umma_commit_pair(&tmem_full_bar[buffer], 3);
+              GG_TRACE_EVENT(1, trace_cursor, 3);
+              buffer ^= 1u;
+              if (buffer == 0) empty_parity ^= 1u;
+            }
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          continue;
+        }
         int remaining = ksteps;
         for (int slab = 0; slab < slabs && ok; ++slab) {
           if (!mbar_test(&full_bar[stage], phase) &&
@@ -353,9 +416,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int sb_col = n0 + tid;
       const bool sb_ok = tid < BN && sb_col < p.n;
 
-      float acc[kNC];
+      float2 acc[kNC / 2];
 #pragma unroll
-      for (int i = 0; i < kNC; ++i) acc[i] = 0.0f;
+      for (int i = 0; i < kNC / 2; ++i) acc[i] = make_float2(0.0f, 0.0f);
 
       // Stage the first group's column scales; later groups are prefetched one ahead.
       if (tid < BN) sb_ring[tid] = sb_ok ? sb_base[sb_col * p.sb_sn] : 0.0f;
@@ -386,6 +449,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int chunk = 0; chunk < kNC / 32; ++chunk) {
           if (!ok) break;
           tmem_ld_wait();
+          if (chunk == 0 && threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 4);
           if (chunk + 1 < kNC / 32) {
             if (chunk & 1) tmem_ld_32x32b_x32(taddr + (chunk + 1) * 32, partial_a);
             else tmem_ld_32x32b_x32(taddr + (chunk + 1) * 32, partial_b);
@@ -398,8 +462,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               else mbar_arrive_cluster(&tmem_empty_bar[buffer], 0);
             }
           }
-          if (chunk & 1) promote32(partial_b, sa, sb_slot + chunk * 32, acc + chunk * 32);
-          else promote32(partial_a, sa, sb_slot + chunk * 32, acc + chunk * 32);
+          if (chunk & 1) promote32(partial_b, sa, sb_slot + chunk * 32, acc + chunk * 16);
+          else promote32(partial_a, sa, sb_slot + chunk * 32, acc + chunk * 16);
         }
         if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 2);
         if (tid < BN) sb_ring[((g + 1) & 1) * BN + tid] = sb_next;
@@ -411,10 +475,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int remaining = p.n - (n0 + col_base);
 #pragma unroll
         for (int j = 0; j < kNC; j += 8) {
+          const float values[8] = {acc[j / 2].x,     acc[j / 2].y,     acc[j / 2 + 1].x,
+                                   acc[j / 2 + 1].y, acc[j / 2 + 2].x, acc[j / 2 + 2].y,
+                                   acc[j / 2 + 3].x, acc[j / 2 + 3].y};
           if (j + 8 <= remaining && p.c_vector_ok) {
-            store_row_vector8<OutT>(c_row + j, acc + j);
+            store_row_vector8<OutT>(c_row + j, values);
           } else if (j < remaining) {
-            store_row_chunk<OutT>(c_row + j, acc + j, min(8, remaining - j));
+            store_row_chunk<OutT>(c_row + j, values, min(8, remaining - j));
           }
         }
       }

@@ -287,9 +287,9 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
         const int sb_col = p.interleaved ? 2 * channel0 + tid
                                          : (tid < 128 ? channel0 + tid
                                                       : p.intermediate + channel0 + tid - 128);
-        float acc[128];
+        float2 acc2[64];
 #pragma unroll
-        for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < 64; ++i) acc2[i] = make_float2(0.0f, 0.0f);
         sb_ring[tid] = sb_base[sb_col];
         float sa_next = row_ok ? sa_row[0] : 0.0f;
         named_barrier_sync(1, 256);
@@ -319,29 +319,33 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
             tmem_ld_32x32b_x32(taddr + column0, partial_a);
             tmem_ld_wait();
             tmem_ld_32x32b_x32(taddr + column1, partial_b);
-            promote32(partial_a, sa, sb_slot + column0, acc);
+            promote32(partial_a, sa, sb_slot + column0, acc2);
             tmem_ld_wait();
             tmem_ld_32x32b_x32(taddr + column2, partial_a);
-            promote32(partial_b, sa, sb_slot + column1, acc + 32);
+            promote32(partial_b, sa, sb_slot + column1, acc2 + 16);
             tmem_ld_wait();
             tmem_ld_32x32b_x32(taddr + column3, partial_b);
-            promote32(partial_a, sa, sb_slot + column2, acc + 64);
+            promote32(partial_a, sa, sb_slot + column2, acc2 + 32);
             tmem_ld_wait();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
-            promote32(partial_b, sa, sb_slot + column3, acc + 96);
+            promote32(partial_b, sa, sb_slot + column3, acc2 + 48);
           }
           sb_ring[((g + 1) & 1) * BN + tid] = sb_next;
           named_barrier_sync(1, 256);
         }
 
-        // SwiGLU on the rounded gate/up values; h overwrites acc[0..63].
+        // SwiGLU on the rounded gate/up values.  Accumulator i is column i of this thread's
+        // 128: split layout = gate c at i = c and up c at i = 64 + c; interleaved = 2c, 2c + 1.
+        float acc[64];
         float amax = 0.0f;
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
-          const float gate = round_through<RoundT>(p.interleaved ? acc[2 * c] : acc[c]);
-          const float up = round_through<RoundT>(p.interleaved ? acc[2 * c + 1] : acc[64 + c]);
+          const float gate_split = (c & 1) ? acc2[c / 2].y : acc2[c / 2].x;
+          const float up_split = (c & 1) ? acc2[32 + c / 2].y : acc2[32 + c / 2].x;
+          const float gate = round_through<RoundT>(p.interleaved ? acc2[c].x : gate_split);
+          const float up = round_through<RoundT>(p.interleaved ? acc2[c].y : up_split);
           const float h = swiglu_value(gate, up);
           acc[c] = h;
           amax = fmaxf(amax, fabsf(h));
