@@ -8,7 +8,7 @@
 // to FP32 once, one fused multiply-add per group, one final cast.
 //
 // Kernel shape (persistent, warp specialised, 384 threads):
-//   warp 8      TMA producer: A tile [128 rows x 128 B of K] and B tile [BN/ctas rows x 128 B]
+//   producer    TMA warp: A tile [128 rows x 128 B of K] and B tile [BN/ctas rows x 128 B]
 //               per stage, 128-byte swizzle, kStages-deep ring guarded by full/empty mbarriers.
 //   warp 9      MMA issuer: tcgen05.mma kind::i8, K = 32 per instruction, INT32 accumulators in
 //               TMEM, two accumulator buffers of BN columns.  The first MMA of every K group
@@ -52,7 +52,7 @@ struct GemmTcParams {
   long long sb_expert_stride;  // elements between experts in scale_b
 };
 
-template <int kCtaGroup, int BN, int kStages>
+template <int kCtaGroup, int BN, int kStages, int kPromoWarps = 8>
 struct GemmTcShape {
   static constexpr int kBM = 128;                       // rows per CTA
   static constexpr int kBK = 128;                       // bytes of K per stage
@@ -64,7 +64,20 @@ struct GemmTcShape {
   static constexpr int kScaleBytes = 2 * BN * 4;
   static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kBarrierBytes;
-  static constexpr int kThreads = 384;
+  static constexpr int kThreads = (kPromoWarps + 4) * 32;   // + producer, MMA, two spares
+  static constexpr int kColumnsPerThread = BN / (kPromoWarps / 4);
+  static constexpr int kDrainWidth = kPromoWarps == 16 ? 16 : 32;  // columns per tcgen05.ld
+  static constexpr int kPromoRegisters = kPromoWarps == 16 ? 104 : 216;
+  static constexpr int kAuxRegisters = kPromoWarps == 16 ? 48 : 64;
+  // setmaxnreg can only hand the promotion warps registers that the four other warps of the
+  // same CTA released: (promo - launch) * promo threads <= (launch - aux) * 128, where launch
+  // is the per-thread count the kernel starts with under its launch bound.
+  static constexpr int kLaunchRegisters = kPromoWarps == 16 ? 96 : 168;
+  static_assert((kPromoRegisters - kLaunchRegisters) * kPromoWarps * 32 <=
+                    (kLaunchRegisters - kAuxRegisters) * 128,
+                "register reallocation exceeds what the auxiliary warps release");
+  static_assert(kPromoWarps == 8 || kPromoWarps == 16, "promotion warps come in groups of four");
+  static_assert(kColumnsPerThread % kDrainWidth == 0, "tile too narrow for the warp count");
   static_assert(BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
 };
 
@@ -129,13 +142,14 @@ __device__ __forceinline__ void store_row_vector8(OutT* dst, const float* v) {
   }
 }
 
-// One promotion step over 32 drained columns: acc = fmaf(float(partial), sa*sb, acc), two
+// One promotion step over kWidth drained columns: acc = fmaf(float(partial), sa*sb, acc), two
 // columns per packed FP32 instruction (IEEE round-to-nearest per lane, bit-identical to the
 // scalar mul.rn / fma.rn).  GG_SCALAR_PROMOTE selects the scalar form for comparison.
-__device__ __forceinline__ void promote32(const uint32_t (&partial)[32], float sa,
-                                          const float* __restrict__ sb_smem, float2* acc) {
+template <int kWidth>
+__device__ __forceinline__ void promote(const uint32_t (&partial)[kWidth], float sa,
+                                        const float* __restrict__ sb_smem, float2* acc) {
 #pragma unroll
-  for (int j = 0; j < 32; j += 4) {
+  for (int j = 0; j < kWidth; j += 4) {
     const float4 sb = *reinterpret_cast<const float4*>(sb_smem + j);
 #ifdef GG_CONVERT_I2F
     const float2 p01 = make_float2(__int2float_rn(static_cast<int>(partial[j + 0])),
@@ -169,12 +183,15 @@ __device__ __forceinline__ void promote32(const uint32_t (&partial)[32], float s
   }
 }
 
-template <int kCtaGroup, int BN, int kStages, typename OutT, bool kGrouped>
-__global__ void __launch_bounds__(384, 1)
+template <int kCtaGroup, int BN, int kStages, typename OutT, bool kGrouped, int kPromoWarps>
+__global__ void __launch_bounds__((kPromoWarps + 4) * 32, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmTcParams p) {
-  using Shape = GemmTcShape<kCtaGroup, BN, kStages>;
-  constexpr int kNC = BN / 2;  // columns owned by one promotion thread
+  using Shape = GemmTcShape<kCtaGroup, BN, kStages, kPromoWarps>;
+  constexpr int kNC = Shape::kColumnsPerThread;   // columns owned by one promotion thread
+  constexpr int kDW = Shape::kDrainWidth;
+  constexpr int kProducerWarp = kPromoWarps, kMmaWarp = kPromoWarps + 1;
+  constexpr int kPromoThreads = kPromoWarps * 32;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -207,27 +224,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tmem_full_bar[i], 1);
-      mbar_init(&tmem_empty_bar[i], 8 * kCtaGroup);
+      mbar_init(&tmem_empty_bar[i], kPromoWarps * kCtaGroup);
     }
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
   }
   if constexpr (kCtaGroup == 2) cluster_sync_all();
-  if (warp == 9) tmem_alloc<kCtaGroup>(tmem_holder, Shape::kTmemColumns);
+  if (warp == kMmaWarp) tmem_alloc<kCtaGroup>(tmem_holder, Shape::kTmemColumns);
   tcgen05_fence_before();
   __syncthreads();
   if constexpr (kCtaGroup == 2) cluster_sync_all();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  // Warps 8-11 (producer, MMA issuer, two spares) give registers to the promotion warps.
-  if (warp >= 8) {
-  setmaxnreg_dec<64>();
-  if (warp == 8) {
+  // The last four warps (producer, MMA issuer, two spares) give registers to the promotion warps.
+  if (warp >= kPromoWarps) {
+  setmaxnreg_dec<Shape::kAuxRegisters>();
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
@@ -272,7 +289,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     // One thread issues every MMA; the loop body is kept to a handful of instructions per
     // MMA (descriptor low words advance by constants, ring positions are running counters).
@@ -383,11 +400,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   }
   } else {
-    setmaxnreg_inc<216>();
+    setmaxnreg_inc<Shape::kPromoRegisters>();
     // ------------------------------------------------------------ promotion warps
-    const int half = warp >> 2;           // which half of the BN columns
+    const int half = warp >> 2;           // which slice of the BN columns
     const int quarter = warp & 3;         // TMEM lane quarter this warp may read
-    const int tid = threadIdx.x;          // 0..255
+    const int tid = threadIdx.x;          // 0..kPromoThreads-1
     const int row_in_cta = quarter * 32 + lane;
     const int col_base = half * kNC;
     uint32_t group_sequence = 0;
@@ -423,7 +440,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // Stage the first group's column scales; later groups are prefetched one ahead.
       if (tid < BN) sb_ring[tid] = sb_ok ? sb_base[sb_col * p.sb_sn] : 0.0f;
       float sa_next = row_ok ? p.scale_a[row * p.sa_sm] : 0.0f;
-      named_barrier_sync(1, 256);
+      named_barrier_sync(1, kPromoThreads);
 
       for (int g = 0; g < groups; ++g, ++group_sequence) {
         const float sa = sa_next;
@@ -443,16 +460,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t taddr =
             tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN + col_base;
         // Two register buffers: the load of chunk c+1 is in flight while chunk c is promoted.
-        uint32_t partial_a[32], partial_b[32];
-        if (ok) tmem_ld_32x32b_x32(taddr, partial_a);
+        uint32_t partial_a[kDW], partial_b[kDW];
+        if (ok) tmem_ld_columns<kDW>(taddr, partial_a);
 #pragma unroll
-        for (int chunk = 0; chunk < kNC / 32; ++chunk) {
+        for (int chunk = 0; chunk < kNC / kDW; ++chunk) {
           if (!ok) break;
           tmem_ld_wait();
           if (chunk == 0 && threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 4);
-          if (chunk + 1 < kNC / 32) {
-            if (chunk & 1) tmem_ld_32x32b_x32(taddr + (chunk + 1) * 32, partial_a);
-            else tmem_ld_32x32b_x32(taddr + (chunk + 1) * 32, partial_b);
+          if (chunk + 1 < kNC / kDW) {
+            if (chunk & 1) tmem_ld_columns<kDW>(taddr + (chunk + 1) * kDW, partial_a);
+            else tmem_ld_columns<kDW>(taddr + (chunk + 1) * kDW, partial_b);
           } else {
             // All of this warp's TMEM reads for the buffer are done: hand it back.
             tcgen05_fence_before();
@@ -462,12 +479,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               else mbar_arrive_cluster(&tmem_empty_bar[buffer], 0);
             }
           }
-          if (chunk & 1) promote32(partial_b, sa, sb_slot + chunk * 32, acc + chunk * 16);
-          else promote32(partial_a, sa, sb_slot + chunk * 32, acc + chunk * 16);
+          if (chunk & 1) promote<kDW>(partial_b, sa, sb_slot + chunk * kDW, acc + chunk * kDW / 2);
+          else promote<kDW>(partial_a, sa, sb_slot + chunk * kDW, acc + chunk * kDW / 2);
         }
         if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 2);
         if (tid < BN) sb_ring[((g + 1) & 1) * BN + tid] = sb_next;
-        named_barrier_sync(1, 256);
+        named_barrier_sync(1, kPromoThreads);
         if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 3);
       }
       if (row_ok && ok) {
@@ -491,7 +508,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tcgen05_fence_before();
   __syncthreads();
   if constexpr (kCtaGroup == 2) cluster_sync_all();
-  if (warp == 9) tmem_dealloc<kCtaGroup>(tmem_base, Shape::kTmemColumns);
+  if (warp == kMmaWarp) tmem_dealloc<kCtaGroup>(tmem_base, Shape::kTmemColumns);
 }
 
 }  // namespace gg

@@ -319,18 +319,18 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
             tmem_ld_32x32b_x32(taddr + column0, partial_a);
             tmem_ld_wait();
             tmem_ld_32x32b_x32(taddr + column1, partial_b);
-            promote32(partial_a, sa, sb_slot + column0, acc2);
+            promote<32>(partial_a, sa, sb_slot + column0, acc2);
             tmem_ld_wait();
             tmem_ld_32x32b_x32(taddr + column2, partial_a);
-            promote32(partial_b, sa, sb_slot + column1, acc2 + 16);
+            promote<32>(partial_b, sa, sb_slot + column1, acc2 + 16);
             tmem_ld_wait();
             tmem_ld_32x32b_x32(taddr + column3, partial_b);
-            promote32(partial_a, sa, sb_slot + column2, acc2 + 32);
+            promote<32>(partial_a, sa, sb_slot + column2, acc2 + 32);
             tmem_ld_wait();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
-            promote32(partial_b, sa, sb_slot + column3, acc2 + 48);
+            promote<32>(partial_b, sa, sb_slot + column3, acc2 + 48);
           }
           sb_ring[((g + 1) & 1) * BN + tid] = sb_next;
           named_barrier_sync(1, 256);

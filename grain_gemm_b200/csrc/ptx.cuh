@@ -111,6 +111,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                : "memory");
 }
 
+// Upper bound, in nanoseconds, for which one try_wait may keep the thread suspended before it
+// reports "not yet"; keeps waiting warps from burning issue slots on polling.
+#ifndef GG_TRY_WAIT_SUSPEND_NS
+#define GG_TRY_WAIT_SUSPEND_NS 20000
+#endif
+constexpr uint32_t kTryWaitSuspendNs = GG_TRY_WAIT_SUSPEND_NS;
+
 // Single non-blocking probe of a phase parity.
 __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   uint32_t done;
@@ -138,11 +145,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(done)
-        : "r"(addr), "r"(parity)
+        : "r"(addr), "r"(parity), "r"(kTryWaitSuspendNs)
         : "memory");
     if (done) return true;
     if ((spin & 0x3ffu) == 0x3ffu) {
@@ -316,6 +323,25 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
         "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+
+// Same for 16 columns.
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+template <int kWidth>
+__device__ __forceinline__ void tmem_ld_columns(uint32_t taddr, uint32_t (&r)[kWidth]) {
+  static_assert(kWidth == 16 || kWidth == 32, "unsupported drain width");
+  if constexpr (kWidth == 32) tmem_ld_32x32b_x32(taddr, r);
+  else tmem_ld_32x32b_x16(taddr, r);
 }
 
 __device__ __forceinline__ void tmem_ld_wait() {

@@ -103,7 +103,7 @@ def get_kernel_config(a, b, *, group_size=256, output_dtype=torch.bfloat16,
         variant = _select(a, b, None, group_size, output_dtype)
     name = _loader.VARIANT_NAMES[variant]
     pair = name.startswith("tc_pair")
-    block_n = int(name.rsplit("n", 1)[1]) if name.startswith("tc") else 32
+    block_n = int(name.split("_n", 1)[1].split("_")[0]) if name.startswith("tc") else 32
     return dict(policy="sm100_native", compute_capability=list(capability), backend="cuda",
                 variant=name, block_m=(256 if pair else 128) if name.startswith("tc") else 32,
                 block_n=block_n, cta_group=2 if pair else 1,
