@@ -39,6 +39,8 @@ _SIGNATURES = {
     "grain_cute_g256": (_INT, [_VOID] * 5 + [_INT] * 4 + [_VOID]),
     "gg_moe_route_workspace_bytes": (_SIZE, [_INT] * 3),
     "gg_moe_route": (_INT, [_VOID, _INT, _VOID, _INT, _INT, _INT] + [_VOID] * 7 + [_SIZE, _VOID]),
+    "gg_moe_route_noalloc": (_INT, [_VOID, _INT, _VOID, _INT, _INT, _INT] + [_VOID] * 6 + [_VOID]),
+    "gg_moe_route_noalloc_capacity_bytes": (_SIZE, []),
     "gg_moe_tile_capacity": (_INT, [_INT] * 3),
     "gg_moe_tiles": (_INT, [_VOID, _INT, _INT, _INT, _VOID, _VOID, _VOID]),
     "gg_moe_gate_up": (_INT, [_VOID] * 8 + [_INT, _INT] + [_VOID] * 3 + [_INT] * 7 + [_VOID]),

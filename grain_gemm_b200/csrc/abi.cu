@@ -7,6 +7,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/grain_gemm_b200.h"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
@@ -238,6 +240,10 @@ int gg_abi_version(void) { return gg::kAbiVersion; }
 const char* gg_error_string(int status) {
   if (status == 0) return "success";
   if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  if (status == GG_STATUS_STATIC_SCRATCH_TOO_SMALL) {
+    return "problem too large for the library's static scratch (use the entry point that takes "
+           "a caller workspace)";
+  }
   if (status <= -10000) {
     static thread_local char text[64];
     snprintf(text, sizeof(text), "tensor map encoding failed (CUresult %d)", -10000 - status);
@@ -352,6 +358,50 @@ int gg_moe_route(const void* ids, int ids_are_i64, const void* mask, int tokens,
   gg::route_place_kernel<<<chunks, gg::kRouteChunk, smem, stream>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---- routing without any allocation -----------------------------------------------------
+//
+// Scratch for gg_moe_route_noalloc lives in the library image: every GPU that loads the
+// library carries these 2 MiB until the process exits.
+static constexpr size_t kStaticRouteScratchInts = 512 * 1024;
+static __device__ __align__(256) int g_static_route_scratch[kStaticRouteScratchInts];
+
+// Device address of the static scratch for the current device.  In host code the array's
+// name is only a handle; the address a kernel can use comes from cudaGetSymbolAddress, asked
+// once per device while that device is current.
+static int static_route_scratch(int** out) {
+  static int* address[64] = {nullptr};
+  static std::mutex guard;
+  int device = 0;
+  cudaError_t error = cudaGetDevice(&device);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  if (device < 0 || device >= 64) return static_cast<int>(cudaErrorInvalidDevice);
+  std::lock_guard<std::mutex> lock(guard);
+  if (address[device] == nullptr) {
+    void* pointer = nullptr;
+    error = cudaGetSymbolAddress(&pointer, g_static_route_scratch);
+    if (error != cudaSuccess) return static_cast<int>(error);
+    address[device] = static_cast<int*>(pointer);
+  }
+  *out = address[device];
+  return 0;
+}
+
+int gg_moe_route_noalloc(const void* ids, int ids_are_i64, const void* mask, int tokens, int top_k,
+                         int experts, void* effective_ids, void* order, void* inverse, void* counts,
+                         void* offsets, void* statistics, void* stream) {
+  if (tokens < 0 || top_k <= 0 || experts <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  const size_t needed = gg_moe_route_workspace_bytes(tokens, top_k, experts);
+  if (needed > kStaticRouteScratchInts * sizeof(int)) return GG_STATUS_STATIC_SCRATCH_TOO_SMALL;
+  int* scratch = nullptr;
+  const int status = static_route_scratch(&scratch);
+  if (status) return status;
+  return gg_moe_route(ids, ids_are_i64, mask, tokens, top_k, experts, effective_ids, order, inverse,
+                      counts, offsets, statistics, scratch, kStaticRouteScratchInts * sizeof(int),
+                      stream);
+}
+
+size_t gg_moe_route_noalloc_capacity_bytes(void) { return kStaticRouteScratchInts * sizeof(int); }
 
 int gg_moe_tile_capacity(int assignments, int experts, int tile_rows) {
   if (assignments < 0 || experts <= 0 || tile_rows <= 0) return 0;

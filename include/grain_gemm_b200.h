@@ -97,6 +97,38 @@ int gg_moe_route(const void* ids, int ids_are_i64, const void* mask, int tokens,
                  void* offsets, void* statistics, void* workspace, size_t workspace_bytes,
                  void* stream);
 
+/*
+ * gg_moe_route for callers that cannot allocate device memory.  This entry point has no
+ * counterpart in the reference.  Some hosts of this library are not allowed to call
+ * cudaMalloc (or an allocator built on it) at the point where routing runs: an inference
+ * server that hands out all of its device memory at start-up and forbids later growth, a
+ * plugin whose host gives it no allocator, or a latency-critical loop that must not hit the
+ * implicit device-wide synchronisation of an allocation.  They cannot provide the
+ * `workspace` that gg_moe_route asks for, so this variant keeps the scratch inside the
+ * library, in a fixed array in device memory that is part of the loaded module:
+ *  - capacity gg_moe_route_noalloc_capacity_bytes() = 2 MiB per GPU, held by every GPU that
+ *    loads the library until the process exits;
+ *  - the problem must satisfy gg_moe_route_workspace_bytes(T, R, E) <= that capacity
+ *    (for example 131072 assignments with up to 4094 experts); anything larger returns
+ *    GG_STATUS_STATIC_SCRATCH_TOO_SMALL and launches nothing;
+ *  - it calls no cudaMalloc, cudaFree or any other allocating routine; inputs and outputs
+ *    are still the caller's;
+ *  - the first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current) and remembers it; make that first
+ *    call before starting any stream capture on the device;
+ *  - every call on a device shares the one array, which keeps whatever the previous call
+ *    left in it.  The routing kernels overwrite every scratch word they later read, so
+ *    nothing has to be cleared between calls, but two calls whose kernels overlap on the
+ *    GPU (different streams, or different host threads on one device) race on it: issue
+ *    them on one stream or order them with events.
+ * Outputs are identical to gg_moe_route's.
+ */
+#define GG_STATUS_STATIC_SCRATCH_TOO_SMALL (-20001)
+int gg_moe_route_noalloc(const void* ids, int ids_are_i64, const void* mask, int tokens, int top_k,
+                         int experts, void* effective_ids, void* order, void* inverse, void* counts,
+                         void* offsets, void* statistics, void* stream);
+size_t gg_moe_route_noalloc_capacity_bytes(void);
+
 /* Entries tile_expert / tile_row must hold for S assignments, E experts, tiles of tile_rows. */
 int gg_moe_tile_capacity(int assignments, int experts, int tile_rows);
 
