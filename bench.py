@@ -9,7 +9,8 @@ inside the timed region.
 
 N > 1 (``torchrun``): the GEMM is sharded along N with no data-path collective (every rank
 owns its own 8192-column block of B and of C; A and scale_a are replicated), weak scaling;
-the MoE FFN (``--workload moe``) is expert-parallel with NCCL all-to-all.
+the MoE FFN timed beside it (``--moe-config``, reported under ``"moe"``) is expert-parallel
+with NCCL all-to-all for dispatch and combine.
 
 ``--impl reference`` times the reference's CPU path for the same metric: the CPU oracle
 (``oracle/``, a restatement of the reference's arithmetic; the reference ships no compiled
@@ -40,10 +41,12 @@ NCU_TRAFFIC_BYTES = {"gemm_g256_m8192_n8192_k8192_bf16": None}
 def parse():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="gemm", choices=["gemm", "moe"])
+    parser.add_argument("--moe-config", default="large",
+                        help="MoE FFN configuration timed beside the GEMM ('none' skips it)")
+    parser.add_argument("--moe-steps", type=int, default=10)
     parser.add_argument("--m", type=int, default=8192)
     parser.add_argument("--n", type=int, default=8192)
     parser.add_argument("--k", type=int, default=8192)
@@ -79,7 +82,7 @@ class ClockSampler:
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.device_index)],
+                 "-lms", "50", "-i", str(self.device_index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -180,6 +183,79 @@ def run_reference_arm(args, rank):
     print(json.dumps(line))
 
 
+def run_moe(args, rank, world, device, barrier):
+    """Times the MoE FFN: single GPU at world == 1, expert parallel (NCCL all-to-all) beyond.
+    Returns the rank-0 report (None on other ranks)."""
+    import torch.distributed as dist
+
+    from grain_gemm_b200 import bench_moe, distributed, moe
+
+    name = args.moe_config
+    config = bench_moe.CONFIGS[name]
+    case = bench_moe.make_case(name, device, rank=rank, world=world)
+
+    def step(tensors):
+        if world == 1:
+            return moe.moe_ffn(**tensors)
+        return distributed.moe_ffn_expert_parallel(**tensors, num_experts=config["experts"])
+
+    steps = max(1, args.moe_steps)
+    for _ in range(3):
+        step(case)
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step(case)
+    stop.record()
+    barrier()
+    elapsed = torch.tensor([start.elapsed_time(stop) / steps], device=device)
+
+    # End to end: the per-token inputs come from pinned host memory, the result goes back.
+    token_names = ("hidden_states", "scale_x", "topk_weights", "topk_ids")
+    host = {n: case[n].cpu().pin_memory() for n in token_names}
+    host_out = torch.empty(case["hidden_states"].shape, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        tensors = dict(case)
+        for n in token_names:
+            tensors[n] = host[n].to(device, non_blocking=True)
+        host_out.copy_(step(tensors), non_blocking=True)
+
+    e2e_step()
+    barrier()
+    start.record()
+    for _ in range(steps):
+        e2e_step()
+    stop.record()
+    barrier()
+    e2e_elapsed = torch.tensor([start.elapsed_time(stop) / steps], device=device)
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        dist.all_reduce(e2e_elapsed, op=dist.ReduceOp.MAX)
+    stages = bench_moe.time_stages(case, steps=3, warmup=1) if world == 1 else None
+    if rank != 0:
+        return None
+    ms, e2e_ms = float(elapsed.item()), float(e2e_elapsed.item())
+    tokens = config["tokens"]
+    report = {
+        "metric": "moe_ffn_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": steps, "ms_per_step": ms, "scaling": "strong",
+        "useful_tops": bench_moe.useful_ops(name) / (ms * 1e-3) / 1e12,
+        "config": {"workload": f"moe_{name}", **{k: v for k, v in config.items()},
+                   "parallelism": "single" if world == 1 else f"ep{world}_nccl_all_to_all"},
+        "algorithmic_bytes": bench_moe.algorithmic_bytes(name),
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": world * sum(t.numel() * t.element_size() for t in host.values()),
+                "d2h_bytes_per_step": world * host_out.numel() * host_out.element_size(),
+                "ms_per_step": e2e_ms},
+        "gpu_launches_per_step": 7 if world == 1 else 12,
+    }
+    if stages is not None:
+        report["stage_ms"] = stages
+    return report
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -188,11 +264,6 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
-    if args.workload == "moe":
-        from grain_gemm_b200 import bench_moe
-        bench_moe.run(args, rank, world, local_rank)
-        return
-
     import torch.distributed as dist
     from grain_gemm_b200 import _loader, gemm
 
@@ -239,6 +310,7 @@ def main():
     if status:
         raise SystemExit(f"a kernel reported device status {status:#x}")
     tops = 2.0 * m * n * world * k / (ms_per_step * 1e-3) / 1e12
+    kernel_name = gemm.get_kernel_config(a, b, group_size=g)["variant"]
 
     # End to end through the public API with host operands.
     e2e = None
@@ -271,6 +343,12 @@ def main():
         e2e = {"value": 2.0 * m * n * world * k / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms}
 
+    moe_result = None
+    if args.moe_config != "none":
+        del a, w, scale_a, scale_b, out
+        torch.cuda.empty_cache()
+        moe_result = run_moe(args, rank, world, device, barrier)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -287,7 +365,7 @@ def main():
         "frac_of_nominal_4500": per_gpu_tops / 4500.0,
         "algorithmic_ops_per_launch": 2.0 * m * n * k,
         "algorithmic_bytes_per_launch": gemm_bytes(m, n, k, g),
-        "kernel": gemm.get_kernel_config(a, b, group_size=g)["variant"],
+        "kernel": kernel_name,
     }
     line = {
         "metric": "g256_gemm_effective_int8_tops", "value": tops, "unit": "TOPS", "n_gpus": world,
@@ -301,6 +379,8 @@ def main():
     }
     if e2e is not None:
         line["e2e"] = e2e
+    if moe_result is not None:
+        line["moe"] = moe_result
     if world == 1 and not args.skip_cpu_baseline:
         cpu_tops, seconds, rows, threads = cpu_gemm_sample(m, n, k, g)
         line["cpu_baseline"] = {
