@@ -49,14 +49,28 @@ def make_weights(first_expert, num_experts, hidden, inter, device):
     return w1, w2, s1, s2
 
 
+TOKEN_BLOCK = 16
+
+
 def make_tokens(first_token, num_tokens, hidden, experts, top_k, biased, device, seed=2026):
-    """Quantised activations and routing of tokens [first_token, first_token + num_tokens)."""
-    generator = torch.Generator(device=device).manual_seed(seed * 7919 + first_token)
-    x = torch.randint(-127, 128, (num_tokens, hidden), dtype=torch.int8, device=device,
-                      generator=generator)
-    scale_x = (0.5 + torch.rand((num_tokens, hidden // 256), device=device,
-                                generator=generator)) / 127
-    logits = torch.randn((num_tokens, experts), device=device, generator=generator)
+    """Quantised activations and routing of tokens [first_token, first_token + num_tokens).
+
+    Tokens are generated in blocks of TOKEN_BLOCK from a seed that depends only on the block
+    index, so a shard reproduces exactly the tokens the whole batch would hold."""
+    if first_token % TOKEN_BLOCK or num_tokens % TOKEN_BLOCK:
+        raise ValueError(f"token ranges must be multiples of {TOKEN_BLOCK}")
+    x = torch.empty((num_tokens, hidden), dtype=torch.int8, device=device)
+    scale_x = torch.empty((num_tokens, hidden // 256), dtype=torch.float32, device=device)
+    logits = torch.empty((num_tokens, experts), dtype=torch.float32, device=device)
+    generator = torch.Generator(device=device)
+    for block in range(num_tokens // TOKEN_BLOCK):
+        generator.manual_seed(seed * 7919 + first_token // TOKEN_BLOCK + block)
+        rows = slice(block * TOKEN_BLOCK, (block + 1) * TOKEN_BLOCK)
+        x[rows] = torch.randint(-127, 128, (TOKEN_BLOCK, hidden), dtype=torch.int8, device=device,
+                                generator=generator)
+        scale_x[rows] = (0.5 + torch.rand((TOKEN_BLOCK, hidden // 256), device=device,
+                                          generator=generator)) / 127
+        logits[rows] = torch.randn((TOKEN_BLOCK, experts), device=device, generator=generator)
     if biased:
         logits[:, 0] += 2
     weights, ids = torch.softmax(logits, dim=-1).topk(top_k, dim=-1)
