@@ -47,6 +47,8 @@ def parse():
     parser.add_argument("--moe-config", default="large",
                         help="MoE FFN configuration timed beside the GEMM ('none' skips it)")
     parser.add_argument("--moe-steps", type=int, default=10)
+    parser.add_argument("--only-moe", action="store_true",
+                        help="time only the MoE FFN and print its report as the JSON line")
     parser.add_argument("--m", type=int, default=8192)
     parser.add_argument("--n", type=int, default=8192)
     parser.add_argument("--k", type=int, default=8192)
@@ -274,6 +276,21 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if args.only_moe:
+        report = run_moe(args, rank, world, device, barrier)
+        if rank == 0:
+            report.update({"warmup": 3, "higher_is_better": True, "vs_baseline": None,
+                           "dtype": "int8", "data": "synthetic"})
+            print(json.dumps(report))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     m, n, k, g = args.m, args.n, args.k, args.group_size
     # Rank r owns columns [r*n, (r+1)*n) of B, scale_b and C; A and scale_a are replicated.
     a, w, scale_a, scale_b = make_gemm_inputs(m, n, k, g, 2026, device, weight_seed=3000 + rank)
@@ -283,11 +300,6 @@ def main():
 
     def step():
         gemm.launch(a, b, scale_a, scale_b, out, g, args.variant)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
         step()
