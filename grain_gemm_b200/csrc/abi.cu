@@ -421,6 +421,13 @@ int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, 
   return static_cast<int>(cudaGetLastError());
 }
 
+size_t gg_moe_gate_up_scratch_bytes(int assignments, int intermediate, int tile_rows) {
+  if (tile_rows == 128) {
+    return static_cast<size_t>(gg::sm_count()) * gg::GateUpShape::kStashBytesPerCta;
+  }
+  return static_cast<size_t>(assignments > 0 ? assignments : 0) * 2 * intermediate * 2;
+}
+
 int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const void* scale_w1,
                    const void* order, const void* offsets, const void* tile_expert,
                    const void* tile_row, int tile_capacity, int tile_rows, void* q, void* s,
@@ -435,7 +442,8 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   const long long slots = static_cast<long long>(tokens) * top_k;
   if (tile_rows == 128) {
-    if (!gg::aligned16(x) || !gg::aligned16(w1) || !gg::aligned16(q)) {
+    if (!gg::aligned16(x) || !gg::aligned16(w1) || !gg::aligned16(q) || !gate_up_scratch ||
+        !gg::aligned16(gate_up_scratch)) {
       return static_cast<int>(cudaErrorInvalidValue);
     }
     CUtensorMap map_w;
@@ -452,6 +460,7 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
     p.tile_row = static_cast<const int*>(tile_row);
     p.q = static_cast<int8_t*>(q);
     p.s = static_cast<float*>(s);
+    p.stash = static_cast<float*>(gate_up_scratch);
     p.top_k = top_k; p.hidden = hidden; p.intermediate = intermediate;
     p.max_tiles = tile_capacity; p.interleaved = interleaved;
     const long long items = static_cast<long long>(tile_capacity) * (intermediate / 256);

@@ -16,8 +16,9 @@
 //   warps 8, 10, 11   producers: 16-byte cp.async gather of the x rows (96 threads); lane 0 of
 //             warp 8 also issues the TMA loads of the two weight boxes
 //   warp 9    MMA issuer (tcgen05.mma kind::i8, two TMEM buffers)
-//   warps 0-7 promotion per K group, then SwiGLU; the first sub-tile's h is parked in shared
-//             memory until the second sub-tile supplies the other half of the row maximum.
+//   warps 0-7 promotion per K group, then SwiGLU; the first sub-tile's h is parked in a per-CTA
+//             global scratch (L2 resident) until the second sub-tile supplies the other half of
+//             the row maximum.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -39,23 +40,23 @@ struct GateUpParams {
   const int* tile_row;        // [max_tiles]
   int8_t* q;                  // [S, I]
   float* s;                   // [S, I/256]
+  float* stash;               // [CTAs, 128, 128] parking space for the first sub-tile's h
   int top_k, hidden, intermediate, max_tiles, interleaved;
 };
 
 struct GateUpShape {
-  static constexpr int kStages = 3;
+  static constexpr int kStages = 4;
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBBytes = 256 * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStashPitch = 132;  // floats per parked row (128 + 4: conflict-free float4)
-  static constexpr int kStashBytes = 128 * kStashPitch * 4;
+  static constexpr int kStashPitch = 128;   // floats per parked row
+  static constexpr int kStashBytesPerCta = 128 * kStashPitch * 4;   // in global memory (L2)
   static constexpr int kScaleBytes = 2 * 256 * 4;
   static constexpr int kAmaxBytes = 4 * 128 * 4;
   static constexpr int kTokenBytes = 128 * 4;
   static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStashBytes + kScaleBytes +
-                                    kAmaxBytes + kTokenBytes + kBarrierBytes;
-  static constexpr int kGatherLag = 2;  // slabs whose cp.async may still be in flight
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kAmaxBytes +
+                                    kTokenBytes + kBarrierBytes;
 };
 
 __device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_dst, const void* src, bool valid) {
@@ -63,12 +64,30 @@ __device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_dst, const void*
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(src), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
+// Makes `bar` receive one (pre-counted) arrival once all cp.async issued so far by this
+// thread have completed.
+__device__ __forceinline__ void cp_async_arrive_on(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
 }
-template <int kPending>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+
+// Work item -> (row tile, channel group).  Items of one expert are consecutive and ordered
+// channel-group-major: neighbouring CTAs work on different row tiles of the same expert
+// against the same 256-channel weight block, so that block is read from DRAM once and served
+// from L2 to the other row tiles.  Returns false for items past the last used tile.
+__device__ __forceinline__ bool gate_up_item(const GateUpParams& p, int item, int channel_groups,
+                                             int& tile, int& jg, int& expert) {
+  const int probe = item / channel_groups;
+  expert = p.tile_expert[probe];
+  if (expert < 0) return false;
+  const int begin = p.expert_offsets[expert];
+  const int rows = p.expert_offsets[expert + 1] - begin;
+  const int first = probe - (p.tile_row[probe] - begin) / 128;
+  const int span = (rows + 127) / 128;
+  const int local = item - first * channel_groups;
+  jg = local / span;
+  tile = first + local - jg * span;
+  return true;
 }
 
 template <typename RoundT>
@@ -87,8 +106,10 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* stage_base = smem;
-  float* stash = reinterpret_cast<float*>(smem + kStages * Shape::kStageBytes);
-  float* sb_ring = stash + 128 * Shape::kStashPitch;
+  float* sb_ring = reinterpret_cast<float*>(smem + kStages * Shape::kStageBytes);
+  // The first sub-tile's h waits in global memory (it stays in L2) for the second sub-tile's
+  // half of the row maximum; keeping it out of shared memory buys a fourth operand stage.
+  float* stash = p.stash + static_cast<size_t>(blockIdx.x) * 128 * Shape::kStashPitch;
   float* amax_part = sb_ring + 2 * BN;
   int* tile_tokens = reinterpret_cast<int*>(amax_part + 4 * 128);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(tile_tokens + 128);
@@ -134,13 +155,11 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
     const int gather_id = (warp == 8 ? 0 : warp - 9) * 32 + lane;
     const int chunk = gather_id & 7;
     const int row_group = gather_id >> 3;
-    uint32_t stage = 0, phase = 0, issued = 0;
+    uint32_t stage = 0, phase = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-      const int tile = item / channel_groups;
-      const int jg = item - tile * channel_groups;
-      const int expert = p.tile_expert[tile];
-      if (expert < 0) continue;
+      int tile, jg, expert;
+      if (!gate_up_item(p, item, channel_groups, tile, jg, expert)) continue;
       const int row0 = p.tile_row[tile];
       const int row_end = p.expert_offsets[expert + 1];
       const int8_t* source[11];
@@ -183,29 +202,14 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
                                 (valid_mask >> i) & 1u);
             }
           }
-          cp_async_commit();
-          ++issued;
-          if (issued > Shape::kGatherLag) {
-            // The slab issued kGatherLag iterations ago has landed: publish it.
-            cp_async_wait<Shape::kGatherLag>();
-            fence_proxy_async();
-            const uint32_t done_stage = (stage + kStages - Shape::kGatherLag) % kStages;
-            mbar_arrive(&full_bar[done_stage]);
-          }
+          // The barrier receives this thread's arrival when its copies above have landed;
+          // the thread itself goes straight on to the next slab.
+          cp_async_arrive_on(&full_bar[stage]);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
-      }
-    }
-    // Publish the slabs whose copies were still in flight.
-    cp_async_wait<0>();
-    fence_proxy_async();
-    if (ok) {
-      const uint32_t pending = issued < Shape::kGatherLag ? issued : Shape::kGatherLag;
-      for (uint32_t back = pending; back >= 1; --back) {
-        mbar_arrive(&full_bar[(stage + kStages * 2 - back) % kStages]);
       }
     }
   } else {
@@ -217,8 +221,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
       uint32_t buffer = 0, empty_parity = 1;
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const int tile = item / channel_groups;
-        if (p.tile_expert[tile] < 0) continue;
+        if (p.tile_expert[item / channel_groups] < 0) continue;
         for (int sub = 0; sub < 2 && ok; ++sub) {
           for (int slab = 0; slab < slabs && ok; ++slab) {
             if (!mbar_test(&full_bar[stage], phase) &&
@@ -226,6 +229,9 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
               ok = false;
               break;
             }
+            // The x rows were written by cp.async (generic proxy); order them before the
+            // tensor core's reads (async proxy).
+            fence_proxy_async();
             tcgen05_fence_after();
             const bool group_start = (slab & 1) == 0;
             if (group_start) {
@@ -270,10 +276,8 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
     bool ok = true;
     float* stash_row = stash + row_in_tile * Shape::kStashPitch + half * 64;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-      const int tile = item / channel_groups;
-      const int jg = item - tile * channel_groups;
-      const int expert = p.tile_expert[tile];
-      if (expert < 0) continue;
+      int tile, jg, expert;
+      if (!gate_up_item(p, item, channel_groups, tile, jg, expert)) continue;
       const int row = p.tile_row[tile] + row_in_tile;
       const bool row_ok = row < p.expert_offsets[expert + 1];
       const long long token = row_ok ? p.order[row] / p.top_k : 0;
@@ -374,12 +378,18 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
                 uint32_t words[4];
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
+                  const int c = v * 16 + w * 4;
+                  float h4[4];
+                  if (piece == 0) {
+                    const float4 parked = *reinterpret_cast<const float4*>(stash_row + c);
+                    h4[0] = parked.x; h4[1] = parked.y; h4[2] = parked.z; h4[3] = parked.w;
+                  } else {
+                    h4[0] = acc[c]; h4[1] = acc[c + 1]; h4[2] = acc[c + 2]; h4[3] = acc[c + 3];
+                  }
                   uint32_t packed = 0;
 #pragma unroll
                   for (int b = 0; b < 4; ++b) {
-                    const int c = v * 16 + w * 4 + b;
-                    const float h = piece == 0 ? stash_row[c] : acc[c];
-                    packed |= (static_cast<uint32_t>(quantize_value(h, scale)) & 0xffu) << (8 * b);
+                    packed |= (static_cast<uint32_t>(quantize_value(h4[b], scale)) & 0xffu) << (8 * b);
                   }
                   words[w] = packed;
                 }

@@ -204,9 +204,9 @@ def gate_up_swiglu_quantize(hidden_states, scale_x, w1_linear, scale_gate_up, ro
     device = hidden_states.device
     qh = torch.empty((slots, intermediate), dtype=torch.int8, device=device)
     sh = torch.empty((slots, intermediate // 256), dtype=torch.float32, device=device)
-    scratch = None
-    if routes.tile_rows == CUDA_CORE_TILE_ROWS:
-        scratch = torch.empty((slots, twice_intermediate), dtype=output_dtype, device=device)
+    with torch.cuda.device(device):
+        scratch_bytes = lib.gg_moe_gate_up_scratch_bytes(slots, intermediate, routes.tile_rows)
+    scratch = torch.empty((max(scratch_bytes, 16),), dtype=torch.uint8, device=device)
     _loader.check(lib.gg_moe_gate_up(
         _loader.pointer(hidden_states), _loader.pointer(scale_x), _loader.pointer(w1_linear),
         _loader.pointer(scale_gate_up), _loader.pointer(routes.order),
