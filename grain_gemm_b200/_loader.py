@@ -24,7 +24,7 @@ _SIZE = ctypes.c_size_t
 OUT_DTYPE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 VARIANTS = {
     "auto": 0, "simt": 1, "tc_n256": 2, "tc_n128": 3, "tc_n64": 4,
-    "tc_pair_n256": 5, "tc_pair_n128": 6,
+    "tc_pair_n256": 5, "tc_pair_n128": 6, "tc_splitk": 7,
 }
 VARIANT_NAMES = {value: key for key, value in VARIANTS.items()}
 
@@ -34,6 +34,8 @@ _SIGNATURES = {
     "gg_error_string": (ctypes.c_char_p, [_INT]),
     "grain_cuda_error_string": (ctypes.c_char_p, [_INT]),
     "gg_int8_gemm": (_INT, [_VOID] * 5 + [_INT] * 3 + [_LL] * 9 + [_INT] * 3 + [_VOID]),
+    "gg_int8_gemm_workspace_bytes": (_SIZE, [_INT] * 4),
+    "gg_int8_gemm_ws": (_INT, [_VOID] * 5 + [_INT] * 3 + [_LL] * 9 + [_INT] * 3 + [_VOID, _SIZE, _VOID]),
     "gg_int8_gemm_select": (_INT, [_VOID] * 3 + [_INT] * 3 + [_LL] * 5 + [_INT] * 2),
     "gg_int8_gemm_partials": (_INT, [_VOID] * 6 + [_INT] * 3 + [_LL] * 8 + [_INT, _VOID]),
     "grain_cute_g256": (_INT, [_VOID] * 5 + [_INT] * 4 + [_VOID]),

@@ -90,10 +90,36 @@ static bool tensor_core_layout(const GemmArgs& g) {
          g.b_sn >= g.k && aligned16(g.a) && aligned16(g.b);
 }
 
+// Split-K plan for skinny M: N tiles of 256 columns times k_splits K ranges fill the SMs; the
+// INT32 group dots go through `workspace` and are folded in group order by a second kernel,
+// so the result is bit-identical to the single-pass kernels.
+struct SplitKPlan {
+  int splits, groups_per_split;
+  size_t workspace_bytes;
+};
+
+static SplitKPlan splitk_plan(int m, int n, int k, int group_size) {
+  SplitKPlan plan = {1, 0, 0};
+  const int groups = (k + group_size - 1) / group_size;
+  const int unit = group_size >= 128 ? 1 : 128 / group_size;   // ranges start on 128-byte slabs
+  const int tiles_n = (n + 255) / 256;
+  int splits = sm_count() / (tiles_n > 0 ? tiles_n : 1);
+  if (m > 32 || splits < 2 || groups < 2 * unit) return plan;
+  int per_split = (groups + splits - 1) / splits;
+  per_split = (per_split + unit - 1) / unit * unit;
+  splits = (groups + per_split - 1) / per_split;
+  if (splits < 2) return plan;
+  plan.splits = splits;
+  plan.groups_per_split = per_split;
+  plan.workspace_bytes = static_cast<size_t>(groups) * m * n * sizeof(int);
+  return plan;
+}
+
 static int select_variant(const GemmArgs& g) {
   if (!tensor_core_layout(g)) return GG_VARIANT_SIMT;
   const int sms = sm_count();
   const long long tiles_256 = static_cast<long long>((g.m + 127) / 128) * ((g.n + 255) / 256);
+  if (splitk_plan(g.m, g.n, g.k, g.group_size).splits >= 2) return GG_VARIANT_TC_SPLITK;
   if (g.m > 128 && tiles_256 >= sms) return GG_VARIANT_TC_PAIR_N256;
   if (tiles_256 >= sms) return GG_VARIANT_TC_N256;
   const long long tiles_128 = static_cast<long long>((g.m + 127) / 128) * ((g.n + 127) / 128);
@@ -196,6 +222,7 @@ static int launch_gemm_tc(const GemmArgs& g, int variant, cudaStream_t stream) {
   p.sa_sm = g.sa_sm; p.sa_sg = g.sa_sg; p.sb_sg = g.sb_sg; p.sb_sn = g.sb_sn;
   p.ldc = g.ldc;
   p.group_size = g.group_size;
+  p.k_splits = 1;
   p.tiles_m = (g.m + (pair ? 255 : 127)) / (pair ? 256 : 128);
   p.tiles_n = (g.n + bn - 1) / bn;
   const int out_bytes = g.out_dtype == GG_OUT_FP32 ? 4 : 2;
@@ -210,7 +237,63 @@ static int launch_gemm_tc(const GemmArgs& g, int variant, cudaStream_t stream) {
   }
 }
 
-static int run_gemm(const GemmArgs& g, int variant, cudaStream_t stream) {
+static int launch_gemm_splitk(const GemmArgs& g, void* workspace, size_t workspace_bytes,
+                              cudaStream_t stream) {
+  const SplitKPlan plan = splitk_plan(g.m, g.n, g.k, g.group_size);
+  if (plan.splits < 2 || workspace == nullptr || workspace_bytes < plan.workspace_bytes ||
+      !aligned16(workspace)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  CUtensorMap map_a, map_b;
+  int status = encode_int8_rows(&map_a, g.a, g.m, g.k, g.a_sm, 32);
+  if (status) return status;
+  status = encode_int8_rows(&map_b, g.b, g.n, g.k, g.b_sn, 256);
+  if (status) return status;
+  GemmTcParams p = {};
+  p.m = g.m; p.n = g.n; p.k = g.k;
+  p.group_size = g.group_size;
+  p.tiles_m = 1;
+  p.tiles_n = (g.n + 255) / 256;
+  p.k_splits = plan.splits;
+  p.groups_per_split = plan.groups_per_split;
+  p.partials = static_cast<int*>(workspace);
+  using Shape = GemmTcShape<1, 256, 6, 8, 32>;
+  auto kernel = gemm_tc_kernel<1, 256, 6, float, false, 8, true, 32>;
+  cudaError_t error =
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape::kSmemBytes);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  const int items = p.tiles_n * p.k_splits;
+  const int grid = items < sm_count() ? items : sm_count();
+  kernel<<<grid, Shape::kThreads, Shape::kSmemBytes, stream>>>(map_a, map_b, p);
+  error = cudaGetLastError();
+  if (error != cudaSuccess) return static_cast<int>(error);
+  const int groups = (g.k + g.group_size - 1) / g.group_size;
+  const dim3 fold_grid((g.n + 255) / 256, g.m);
+  const int* partials = static_cast<const int*>(workspace);
+  const float* sa = static_cast<const float*>(g.scale_a);
+  const float* sb = static_cast<const float*>(g.scale_b);
+  switch (g.out_dtype) {
+    case GG_OUT_FP32:
+      fold_partials_kernel<float><<<fold_grid, 256, 0, stream>>>(
+          partials, sa, sb, static_cast<float*>(g.c), g.m, g.n, groups, g.sa_sm, g.sa_sg, g.sb_sg,
+          g.sb_sn, g.ldc);
+      break;
+    case GG_OUT_BF16:
+      fold_partials_kernel<__nv_bfloat16><<<fold_grid, 256, 0, stream>>>(
+          partials, sa, sb, static_cast<__nv_bfloat16*>(g.c), g.m, g.n, groups, g.sa_sm, g.sa_sg,
+          g.sb_sg, g.sb_sn, g.ldc);
+      break;
+    default:
+      fold_partials_kernel<__half><<<fold_grid, 256, 0, stream>>>(
+          partials, sa, sb, static_cast<__half*>(g.c), g.m, g.n, groups, g.sa_sm, g.sa_sg, g.sb_sg,
+          g.sb_sn, g.ldc);
+      break;
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+static int run_gemm(const GemmArgs& g, int variant, cudaStream_t stream, void* workspace = nullptr,
+                    size_t workspace_bytes = 0) {
   if (g.m < 0 || g.n < 0 || g.k < 0 || !valid_group(g.group_size) || g.out_dtype < 0 ||
       g.out_dtype > 2 || g.a_sm <= 0 || g.a_sk <= 0 || g.b_sk <= 0 || g.b_sn <= 0 || g.ldc < g.n) {
     return static_cast<int>(cudaErrorInvalidValue);
@@ -218,7 +301,15 @@ static int run_gemm(const GemmArgs& g, int variant, cudaStream_t stream) {
   if (g.m == 0 || g.n == 0) return 0;
   if (g.k == 0) return static_cast<int>(cudaErrorInvalidValue);  // callers zero-fill instead
   if (!g.a || !g.b || !g.scale_a || !g.scale_b || !g.c) return static_cast<int>(cudaErrorInvalidValue);
-  if (variant == GG_VARIANT_AUTO) variant = select_variant(g);
+  if (variant == GG_VARIANT_AUTO) {
+    variant = select_variant(g);
+    // Without a workspace the skinny shapes stay on the single-pass kernels.
+    if (variant == GG_VARIANT_TC_SPLITK && workspace == nullptr) variant = GG_VARIANT_TC_N64;
+  }
+  if (variant == GG_VARIANT_TC_SPLITK) {
+    if (!tensor_core_layout(g)) return static_cast<int>(cudaErrorInvalidValue);
+    return launch_gemm_splitk(g, workspace, workspace_bytes, stream);
+  }
   if (variant == GG_VARIANT_SIMT) {
     return launch_simt_dtype<false>(simt_params(g), (g.m + kSimtTile - 1) / kSimtTile, g.out_dtype,
                                     stream);
@@ -261,6 +352,21 @@ int gg_int8_gemm(const void* a, const void* b, const void* scale_a, const void* 
   const gg::GemmArgs g = {a, b, scale_a, scale_b, c, m, n, k, a_sm, a_sk, b_sk, b_sn,
                           sa_sm, sa_sg, sb_sg, sb_sn, ldc, group_size, out_dtype};
   return gg::run_gemm(g, variant, static_cast<cudaStream_t>(stream));
+}
+
+size_t gg_int8_gemm_workspace_bytes(int m, int n, int k, int group_size) {
+  if (m <= 0 || n <= 0 || k <= 0 || !gg::valid_group(group_size)) return 0;
+  return gg::splitk_plan(m, n, k, group_size).workspace_bytes;
+}
+
+int gg_int8_gemm_ws(const void* a, const void* b, const void* scale_a, const void* scale_b, void* c,
+                    int m, int n, int k, long long a_sm, long long a_sk, long long b_sk,
+                    long long b_sn, long long sa_sm, long long sa_sg, long long sb_sg,
+                    long long sb_sn, long long ldc, int group_size, int out_dtype, int variant,
+                    void* workspace, size_t workspace_bytes, void* stream) {
+  const gg::GemmArgs g = {a, b, scale_a, scale_b, c, m, n, k, a_sm, a_sk, b_sk, b_sn,
+                          sa_sm, sa_sg, sb_sg, sb_sn, ldc, group_size, out_dtype};
+  return gg::run_gemm(g, variant, static_cast<cudaStream_t>(stream), workspace, workspace_bytes);
 }
 
 int gg_int8_gemm_select(const void* a, const void* b, const void* c, int m, int n, int k,
@@ -547,6 +653,7 @@ int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_
     p.sa_sm = intermediate / 256; p.sa_sg = 1; p.sb_sg = hidden; p.sb_sn = 1;
     p.ldc = hidden;
     p.group_size = 256;
+    p.k_splits = 1;
     p.tiles_m = tile_capacity;
     p.tiles_n = (hidden + bn - 1) / bn;
     p.c_vector_ok = 1;

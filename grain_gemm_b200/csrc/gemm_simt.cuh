@@ -155,4 +155,25 @@ gemm_simt_kernel(const GemmSimtParams p) {
   }
 }
 
+// Second half of the split-K path: folds the INT32 group dots partials[Q][M][N] in group
+// order, C[m,n] = cast(fold_g fmaf(float(p_g), sa[m,g]*sb[g,n], total)); one thread per output.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+fold_partials_kernel(const int* __restrict__ partials, const float* __restrict__ scale_a,
+                     const float* __restrict__ scale_b, OutT* __restrict__ c, int m, int n,
+                     int groups, long long sa_sm, long long sa_sg, long long sb_sg, long long sb_sn,
+                     long long ldc) {
+  const int col = blockIdx.x * 256 + threadIdx.x;
+  const int row = blockIdx.y;
+  if (col >= n) return;
+  float total = 0.0f;
+  const long long plane = static_cast<long long>(m) * n;
+  const int* source = partials + static_cast<long long>(row) * n + col;
+  for (int g = 0; g < groups; ++g) {
+    const float scale = __fmul_rn(scale_a[row * sa_sm + g * sa_sg], scale_b[g * sb_sg + col * sb_sn]);
+    total = __fmaf_rn(__int2float_rn(source[g * plane]), scale, total);
+  }
+  c[static_cast<long long>(row) * ldc + col] = cast_out<OutT>(total);
+}
+
 }  // namespace gg

@@ -50,14 +50,34 @@ struct GemmTcParams {
   const int* tile_row;         // [tiles_m] first row of each row tile
   long long b_rows_per_expert; // N (rows of the Linear weight per expert)
   long long sb_expert_stride;  // elements between experts in scale_b
+  // Split-K dump mode: the K groups are divided over k_splits work items per output tile and
+  // the INT32 group dots go to partials[Q][M][N] instead of being promoted (a second kernel
+  // then folds them in group order).  k_splits == 1 and partials == null otherwise.
+  int k_splits;
+  int groups_per_split;
+  int* partials;
 };
 
-template <int kCtaGroup, int BN, int kStages, int kPromoWarps = 8>
+// K range of one work item (the whole K unless split-K is on).
+struct TileWork {
+  int tm, tn;
+  int group_begin, groups;   // K groups [group_begin, group_begin + groups)
+  int k_begin;               // first K element (a multiple of 128)
+  int ksteps, slabs;         // MMAs (K = 32) and 128-byte slabs in the range
+  bool whole_g256;           // G = 256 and the range is whole groups: fast issue path
+};
+
+template <int kCtaGroup, int BN, int kStages, int kPromoWarps = 8, int kARows = 128>
 struct GemmTcShape {
   static constexpr int kBM = 128;                       // rows per CTA
   static constexpr int kBK = 128;                       // bytes of K per stage
   static constexpr int kBRows = BN / kCtaGroup;         // B rows loaded by each CTA
-  static constexpr int kABytes = kBM * kBK;
+  // Rows of A actually fetched per stage.  Skinny problems (M <= kARows) fetch only that many:
+  // the MMA still reads 128 rows, the rest being whatever follows in the stage (the B tile),
+  // which only feeds accumulator rows that are never stored.
+  static constexpr int kABytes = kARows * kBK;
+  static_assert(kARows % 8 == 0 && kARows <= 128 && (kARows == 128 || kBRows >= 128),
+                "a short A tile needs the B tile behind it to cover the 128 rows the MMA reads");
   static constexpr int kBBytes = kBRows * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemColumns = 2 * BN;
@@ -91,6 +111,28 @@ __device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tile
   const int local = tile - band * band_size;
   tm = first_m + local % band_m;
   tn = local / band_m;
+}
+
+__device__ __forceinline__ TileWork decode_tile(const GemmTcParams& p, int tile) {
+  TileWork w;
+  int split = 0;
+  if (p.k_splits > 1) {
+    const int per_split = p.tiles_m * p.tiles_n;
+    split = tile / per_split;
+    tile -= split * per_split;
+  }
+  tile_coordinates(tile, p.tiles_m, p.tiles_n, w.tm, w.tn);
+  const int total_groups = (p.k + p.group_size - 1) / p.group_size;
+  w.group_begin = split * p.groups_per_split;
+  const int group_end = p.k_splits > 1 ? min(total_groups, w.group_begin + p.groups_per_split)
+                                       : total_groups;
+  w.groups = group_end - w.group_begin;
+  w.k_begin = w.group_begin * p.group_size;
+  const int k_length = min(p.k, group_end * p.group_size) - w.k_begin;
+  w.ksteps = (k_length + 31) / 32;
+  w.slabs = (k_length + 127) / 128;
+  w.whole_g256 = p.group_size == 256 && (k_length & 255) == 0;
+  return w;
 }
 
 template <typename OutT>
@@ -183,11 +225,12 @@ __device__ __forceinline__ void promote(const uint32_t (&partial)[kWidth], float
   }
 }
 
-template <int kCtaGroup, int BN, int kStages, typename OutT, bool kGrouped, int kPromoWarps>
+template <int kCtaGroup, int BN, int kStages, typename OutT, bool kGrouped, int kPromoWarps,
+          bool kDump = false, int kARows = 128>
 __global__ void __launch_bounds__((kPromoWarps + 4) * 32, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmTcParams p) {
-  using Shape = GemmTcShape<kCtaGroup, BN, kStages, kPromoWarps>;
+  using Shape = GemmTcShape<kCtaGroup, BN, kStages, kPromoWarps, kARows>;
   constexpr int kNC = Shape::kColumnsPerThread;   // columns owned by one promotion thread
   constexpr int kDW = Shape::kDrainWidth;
   constexpr int kProducerWarp = kPromoWarps, kMmaWarp = kPromoWarps + 1;
@@ -211,10 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
   const int worker = blockIdx.x / kCtaGroup;
   const int workers = gridDim.x / kCtaGroup;
-  const int total_tiles = p.tiles_m * p.tiles_n;
-  const int groups = (p.k + p.group_size - 1) / p.group_size;
-  const int ksteps = (p.k + 31) / 32;
-  const int slabs = (p.k + Shape::kBK - 1) / Shape::kBK;
+  const int total_tiles = p.tiles_m * p.tiles_n * p.k_splits;
   const int steps_per_group = p.group_size / 32;
 
   if (threadIdx.x == 0) {
@@ -251,8 +291,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       bool ok = true;
       [[maybe_unused]] int trace_cursor = 0;
       for (int tile = worker; tile < total_tiles && ok; tile += workers) {
-        int tm, tn;
-        tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const TileWork work = decode_tile(p, tile);
+        const int tm = work.tm, tn = work.tn;
         int row_a, row_b;
         if constexpr (kGrouped) {
           const int expert = p.tile_expert[tm];
@@ -264,7 +304,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           row_a = (tm * kCtaGroup + static_cast<int>(cta_rank)) * Shape::kBM;
           row_b = tn * BN + static_cast<int>(cta_rank) * Shape::kBRows;
         }
-        for (int slab = 0, x = 0; slab < slabs; ++slab, x += Shape::kBK) {
+        for (int slab = 0, x = work.k_begin; slab < work.slabs; ++slab, x += Shape::kBK) {
           if (!mbar_test(&empty_bar[stage], phase ^ 1u) &&
               !mbar_wait(&empty_bar[stage], phase ^ 1u, kSiteProducerEmpty, abort_flag)) {
             ok = false;
@@ -302,14 +342,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       bool ok = true;
       [[maybe_unused]] int trace_cursor = 0;
       for (int tile = worker; tile < total_tiles && ok; tile += workers) {
+        const TileWork work = decode_tile(p, tile);
         if constexpr (kGrouped) {
-          int tm, tn;
-          tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
-          if (p.tile_expert[tm] < 0) continue;
+          if (p.tile_expert[work.tm] < 0) continue;
         }
-        if (steps_per_group == 8 && (p.k & 255) == 0) {
+        if (work.whole_g256) {
           // G = 256 with whole groups: two slabs per group, no per-MMA bookkeeping.
-          for (int slab = 0; slab < slabs && ok; ++slab) {
+          for (int slab = 0; slab < work.slabs && ok; ++slab) {
             if (!mbar_test(&full_bar[stage], phase) &&
                 !mbar_wait(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
               ok = false;
@@ -351,8 +390,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           continue;
         }
-        int remaining = ksteps;
-        for (int slab = 0; slab < slabs && ok; ++slab) {
+        int remaining = work.ksteps;
+        for (int slab = 0; slab < work.slabs && ok; ++slab) {
           if (!mbar_test(&full_bar[stage], phase) &&
               !mbar_wait(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
             ok = false;
@@ -414,8 +453,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // A failed wait clears `ok` but the loops keep their shape, so that every thread still
     // reaches every named barrier the others wait on.
     for (int tile = worker; tile < total_tiles; tile += workers) {
-      int tm, tn;
-      tile_coordinates(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const TileWork work = decode_tile(p, tile);
+      const int tm = work.tm, tn = work.tn;
+      const int groups = work.groups;
       int row, row_limit;
       const float* sb_base = p.scale_b;
       if constexpr (kGrouped) {
@@ -430,6 +470,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       const int n0 = tn * BN;
       const bool row_ok = row < row_limit;
+      if constexpr (kDump) {
+        // Split-K: hand the exact INT32 group dots to the folding kernel.
+        for (int g = 0; g < groups; ++g, ++group_sequence) {
+          const uint32_t buffer = group_sequence & 1u;
+          if (ok && !mbar_wait(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
+                               kSiteEpilogueTmemFull, abort_flag)) {
+            ok = false;
+          }
+          tcgen05_fence_after();
+          const uint32_t taddr =
+              tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN + col_base;
+          int* destination = p.partials +
+                             (static_cast<long long>(work.group_begin + g) * p.m + row) * p.n + n0 +
+                             col_base;
+          // Rows at or beyond M hold zero-filled operands; a warp whose 32 rows are all
+          // beyond M skips the drain altogether.
+          const bool warp_has_rows = (row - lane) < row_limit;
+          if (ok && warp_has_rows) {
+#pragma unroll
+            for (int chunk = 0; chunk < kNC / 32; ++chunk) {
+              uint32_t partial[32];
+              tmem_ld_32x32b_x32(taddr + chunk * 32, partial);
+              tmem_ld_wait();
+              if (row_ok) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                  const int col = n0 + col_base + chunk * 32 + j;
+                  if (col + 4 <= p.n && (p.n & 3) == 0) {
+                    *reinterpret_cast<uint4*>(destination + chunk * 32 + j) =
+                        make_uint4(partial[j], partial[j + 1], partial[j + 2], partial[j + 3]);
+                  } else {
+                    for (int i = 0; i < 4; ++i) {
+                      if (col + i < p.n) destination[chunk * 32 + j + i] = static_cast<int>(partial[j + i]);
+                    }
+                  }
+                }
+              }
+            }
+          }
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
+        }
+        continue;
+      }
       const int sb_col = n0 + tid;
       const bool sb_ok = tid < BN && sb_col < p.n;
 
@@ -441,6 +526,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (tid < BN) sb_ring[tid] = sb_ok ? sb_base[sb_col * p.sb_sn] : 0.0f;
       float sa_next = row_ok ? p.scale_a[row * p.sa_sm] : 0.0f;
       named_barrier_sync(1, kPromoThreads);
+      static_assert(!kDump || kCtaGroup == 1, "split-K dump runs on single CTAs");
 
       for (int g = 0; g < groups; ++g, ++group_sequence) {
         const float sa = sa_next;

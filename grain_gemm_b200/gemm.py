@@ -103,7 +103,8 @@ def get_kernel_config(a, b, *, group_size=256, output_dtype=torch.bfloat16,
         variant = _select(a, b, None, group_size, output_dtype)
     name = _loader.VARIANT_NAMES[variant]
     pair = name.startswith("tc_pair")
-    block_n = int(name.split("_n", 1)[1].split("_")[0]) if name.startswith("tc") else 32
+    block_n = (256 if name == "tc_splitk" else int(name.split("_n", 1)[1].split("_")[0])
+               if name.startswith("tc") else 32)
     return dict(policy="sm100_native", compute_capability=list(capability), backend="cuda",
                 variant=name, block_m=(256 if pair else 128) if name.startswith("tc") else 32,
                 block_n=block_n, cta_group=2 if pair else 1,
@@ -114,13 +115,20 @@ def launch(a, b, scale_a, scale_b, out, group_size, variant="auto"):
     """Launch the GEMM on torch's current stream (arguments already validated)."""
     m, k = a.shape
     n = b.shape[1]
-    status = _loader.library().gg_int8_gemm(
+    lib = _loader.library()
+    workspace, workspace_bytes = None, 0
+    if variant in ("auto", "tc_splitk"):
+        # Skinny problems split K over the SMs through a caller-owned INT32 workspace.
+        workspace_bytes = lib.gg_int8_gemm_workspace_bytes(m, n, k, group_size)
+        if workspace_bytes:
+            workspace = torch.empty((workspace_bytes,), dtype=torch.uint8, device=a.device)
+    status = lib.gg_int8_gemm_ws(
         _loader.pointer(a), _loader.pointer(b), _loader.pointer(scale_a), _loader.pointer(scale_b),
         _loader.pointer(out), m, n, k,
         *_operand_strides(a, b),
         scale_a.stride(0), scale_a.stride(1), scale_b.stride(0), scale_b.stride(1),
         out.stride(0), group_size, _loader.OUT_DTYPE[out.dtype], _loader.VARIANTS[variant],
-        _loader.stream_pointer(a.device))
+        _loader.pointer(workspace), workspace_bytes, _loader.stream_pointer(a.device))
     _loader.check(status, "gg_int8_gemm")
     return out
 

@@ -33,6 +33,7 @@ extern "C" {
 #define GG_VARIANT_TC_N64 4      /* tcgen05, one CTA per 128 x 64 tile */
 #define GG_VARIANT_TC_PAIR_N256 5 /* tcgen05 cta_group::2, CTA pair per 256 x 256 tile */
 #define GG_VARIANT_TC_PAIR_N128 6 /* tcgen05 cta_group::2, CTA pair per 256 x 128 tile */
+#define GG_VARIANT_TC_SPLITK 7   /* tcgen05, M <= 32: K split over CTAs, INT32 dots folded in order */
 
 /* ABI version of this header; the Python loader refuses a library that reports another. */
 int gg_abi_version(void);
@@ -57,6 +58,21 @@ int gg_int8_gemm(const void* a, const void* b, const void* scale_a, const void* 
                  long long a_sm, long long a_sk, long long b_sk, long long b_sn,
                  long long sa_sm, long long sa_sg, long long sb_sg, long long sb_sn,
                  long long ldc, int group_size, int out_dtype, int variant, void* stream);
+
+/*
+ * gg_int8_gemm with a caller-provided workspace, which skinny problems (M <= 32) use to split
+ * K over all SMs: the exact INT32 group dots are written to the workspace and a second kernel
+ * folds them in group order, so the result is bit-identical to the single-pass kernels.
+ * gg_int8_gemm_workspace_bytes returns the size to provide (0 when no workspace is used);
+ * passing NULL falls back to the single-pass kernels.
+ */
+size_t gg_int8_gemm_workspace_bytes(int m, int n, int k, int group_size);
+int gg_int8_gemm_ws(const void* a, const void* b, const void* scale_a, const void* scale_b, void* c,
+                    int m, int n, int k,
+                    long long a_sm, long long a_sk, long long b_sk, long long b_sn,
+                    long long sa_sm, long long sa_sg, long long sb_sg, long long sb_sn,
+                    long long ldc, int group_size, int out_dtype, int variant,
+                    void* workspace, size_t workspace_bytes, void* stream);
 
 /* Variant gg_int8_gemm would run for these arguments (GG_VARIANT_*), without launching.
  * Backs get_kernel_config (src/grain_gemm/gemm.py:84-178). */

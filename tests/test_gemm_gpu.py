@@ -179,6 +179,18 @@ def test_base_config_and_ragged_k(gg):
         assert torch.equal(run(gg, tensors, 256, dtype), expected)
 
 
+@pytest.mark.parametrize("g", [32, 64, 128, 256])
+@pytest.mark.parametrize("m,n,k", [(1, 2048, 4096), (16, 4096, 4000), (32, 1000, 2080), (7, 8192, 8192)])
+def test_split_k_for_skinny_m_is_bit_exact(gg, m, n, k, g):
+    """K split over the SMs with the INT32 dots folded in group order afterwards."""
+    tensors = linear_case(m, n, k, g, seed=m + g, scale="lognormal")
+    for dtype in (torch.float32, torch.bfloat16):
+        expected = oracle.int8_gemm(*tensors, g, dtype)
+        assert torch.equal(run(gg, tensors, g, dtype, "tc_splitk"), expected)
+    a, b, _, _ = (t.cuda() for t in tensors)
+    assert gg.get_kernel_config(a, b, group_size=g)["variant"] == "tc_splitk"
+
+
 @pytest.mark.parametrize("m", [1, 16, 128])
 def test_skinny_m(gg, m):
     tensors = linear_case(m, 2048, 2048, 128, seed=m, scale="lognormal")

@@ -240,6 +240,37 @@ def test_baseline_config_4_interleaved_decode(moe):
     torch.testing.assert_close(actual.float(), expected.float(), rtol=RTOL, atol=ATOL)
 
 
+def test_baseline_config_5_large_sampled_tokens_and_properties(moe):
+    """T=16384, H=7168, I=2048, E=256, top-8 is far beyond the CPU oracle: check sampled tokens
+    against it (on the experts those tokens use) and two size-independent properties:
+    doubling every routing weight doubles the output exactly, and zero weights give zero."""
+    from grain_gemm_b200 import bench_moe
+
+    case = bench_moe.make_case("large", torch.device("cuda"))
+    out = moe.moe_ffn(**case)
+    doubled = moe.moe_ffn(**{**case, "topk_weights": case["topk_weights"] * 2})
+    assert torch.equal(doubled.float(), out.float() * 2)
+    zeroed = moe.moe_ffn(**{**case, "topk_weights": torch.zeros_like(case["topk_weights"])})
+    assert zeroed.abs().sum() == 0
+
+    tokens = torch.tensor([0, 1, 4097, 8191, 12345, 16383])
+    ids = case["topk_ids"][tokens.cuda()].cpu()
+    used = torch.unique(ids)
+    remap = torch.full((256,), -1, dtype=torch.int64)
+    remap[used] = torch.arange(used.numel())
+    sub = dict(
+        hidden_states=case["hidden_states"][tokens.cuda()].cpu(),
+        scale_x=case["scale_x"][tokens.cuda()].cpu(),
+        topk_weights=case["topk_weights"][tokens.cuda()].cpu(),
+        topk_ids=remap[ids],
+        w_gate_up=case["w_gate_up"][used.cuda()].cpu(),
+        w_down=case["w_down"][used.cuda()].cpu(),
+        scale_gate_up=case["scale_gate_up"][used.cuda()].cpu(),
+        scale_down=case["scale_down"][used.cuda()].cpu())
+    expected = oracle.moe_ffn(**sub)
+    torch.testing.assert_close(out[tokens.cuda()].cpu().float(), expected.float(), rtol=RTOL, atol=ATOL)
+
+
 def test_graph_replay_with_changed_routes(moe):
     case = to_cuda(make_case(64, 512, 256, 8, 2))
     kwargs = {k: v for k, v in case.items()}
