@@ -99,7 +99,12 @@ def _validate(hidden_states, w_gate_up, w_down, topk_weights, topk_ids,
             raise ValueError(f"{name} must have stride {wanted_stride}, got {tensor.stride()}")
         if tensor.device != hidden_states.device or tensor.device.type != "cuda":
             raise ValueError(f"{name} must be on the same CUDA device as hidden_states")
-        if tensor.numel() > 2**31 - 1:
+        # The kernels address weights and their scales with 64-bit offsets (E * 2I and E * H
+        # rows must fit 32 bits), so the reference's 2^31-element limit applies only to the
+        # per-token tensors; the 256-expert, H=7168 configuration fits one GPU.
+        weight_like = name in ("w_gate_up", "w_down", "scale_gate_up", "scale_down")
+        if tensor.numel() > 2**31 - 1 and not (
+                weight_like and tensor.shape[0] * max(tensor.shape[1], tensor.shape[2]) < 2**31):
             raise ValueError(f"{name} exceeds the supported 32-bit indexing range")
         if torch.is_grad_enabled() and tensor.requires_grad:
             raise ValueError("moe_ffn is inference-only; use torch.no_grad() for tensors requiring gradients")
