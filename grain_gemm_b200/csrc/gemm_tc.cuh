@@ -13,6 +13,7 @@
 //   warp 9      MMA issuer: tcgen05.mma kind::i8, K = 32 per instruction, INT32 accumulators in
 //               TMEM, two accumulator buffers of BN columns.  The first MMA of every K group
 //               overwrites the buffer, the last one commits it to the promotion warps.
+//   scale warp  copies each group's scale_b columns and scale_a rows into a shared-memory ring
 //   warps 0-7   promotion: drain the group's INT32 tile with tcgen05.ld (thread = row,
 //               registers = columns), multiply by sa*sb, add into FP32 registers while the
 //               tensor core works on the next group; at the end of the tile cast and store.
@@ -81,8 +82,10 @@ struct GemmTcShape {
   static constexpr int kBBytes = kBRows * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemColumns = 2 * BN;
-  static constexpr int kScaleBytes = 2 * BN * 4;
-  static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kScaleSlots = 4;                 // ring of per-group scale vectors
+  static constexpr int kScaleSlotFloats = BN + 128;     // scale_b columns, then scale_a rows
+  static constexpr int kScaleBytes = kScaleSlots * kScaleSlotFloats * 4;
+  static constexpr int kBarrierBytes = (2 * kStages + 4 + 2 * kScaleSlots) * 8 + 16;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kBarrierBytes;
   static constexpr int kThreads = (kPromoWarps + 4) * 32;   // + producer, MMA, two spares
   static constexpr int kColumnsPerThread = BN / (kPromoWarps / 4);
@@ -154,6 +157,13 @@ __device__ __forceinline__ void store_row_chunk<__half>(__half* dst, const float
 }
 
 template <typename OutT>
+__device__ __forceinline__ OutT cast_out_tc(float v) {
+  if constexpr (sizeof(OutT) == 4) return v;
+  else if constexpr (std::is_same<OutT, __nv_bfloat16>::value) return __float2bfloat16_rn(v);
+  else return __float2half_rn(v);
+}
+
+template <typename OutT>
 __device__ __forceinline__ void store_row_vector8(OutT* dst, const float* v) {
   if constexpr (sizeof(OutT) == 4) {
     float4* d = reinterpret_cast<float4*>(dst);
@@ -192,7 +202,11 @@ __device__ __forceinline__ void promote(const uint32_t (&partial)[kWidth], float
                                         const float* __restrict__ sb_smem, float2* acc) {
 #pragma unroll
   for (int j = 0; j < kWidth; j += 4) {
+#ifdef GG_EXPERIMENT_NO_SB
+    const float4 sb = make_float4(1.0f, 2.0f, 3.0f, 4.0f);
+#else
     const float4 sb = *reinterpret_cast<const float4*>(sb_smem + j);
+#endif
 #ifdef GG_CONVERT_I2F
     const float2 p01 = make_float2(__int2float_rn(static_cast<int>(partial[j + 0])),
                                    __int2float_rn(static_cast<int>(partial[j + 1])));
@@ -225,6 +239,41 @@ __device__ __forceinline__ void promote(const uint32_t (&partial)[kWidth], float
   }
 }
 
+// Promotion of one 16-row x 32-column fragment (tmem_ld_16x256b_x4 layout): this thread holds
+// rows r and r+8 and column pairs 8i+2q, 8i+2q+1.  `sb` are its four column-scale pairs, read
+// once per 32-column block and used for both 16-row halves.
+__device__ __forceinline__ void promote_fragment(const uint32_t (&partial)[16], float sa_low,
+                                                 float sa_high, const float2 (&sb)[4],
+                                                 float2* acc_low, float2* acc_high) {
+  const float2 sa_low2 = make_float2(sa_low, sa_low);
+  const float2 sa_high2 = make_float2(sa_high, sa_high);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 low = make_float2(__int2float_rn(static_cast<int>(partial[4 * i + 0])),
+                                   __int2float_rn(static_cast<int>(partial[4 * i + 1])));
+    const float2 high = make_float2(__int2float_rn(static_cast<int>(partial[4 * i + 2])),
+                                    __int2float_rn(static_cast<int>(partial[4 * i + 3])));
+    acc_low[i] = __ffma2_rn(low, __fmul2_rn(sa_low2, sb[i]), acc_low[i]);
+    acc_high[i] = __ffma2_rn(high, __fmul2_rn(sa_high2, sb[i]), acc_high[i]);
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_pair(OutT* dst, float2 v, bool both, bool aligned) {
+  if (both && aligned) {
+    if constexpr (sizeof(OutT) == 4) {
+      *reinterpret_cast<float2*>(dst) = v;
+    } else if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+      *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v.x, v.y);
+    } else {
+      *reinterpret_cast<__half2*>(dst) = __floats2half2_rn(v.x, v.y);
+    }
+  } else {
+    dst[0] = cast_out_tc<OutT>(v.x);
+    if (both) dst[1] = cast_out_tc<OutT>(v.y);
+  }
+}
+
 template <int kCtaGroup, int BN, int kStages, typename OutT, bool kGrouped, int kPromoWarps,
           bool kDump = false, int kARows = 128>
 __global__ void __launch_bounds__((kPromoWarps + 4) * 32, 1)
@@ -234,19 +283,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr int kNC = Shape::kColumnsPerThread;   // columns owned by one promotion thread
   constexpr int kDW = Shape::kDrainWidth;
   constexpr int kProducerWarp = kPromoWarps, kMmaWarp = kPromoWarps + 1;
-  constexpr int kPromoThreads = kPromoWarps * 32;
+  constexpr int kScaleWarp = kPromoWarps + 2;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* stage_base = smem;
-  float* sb_ring = reinterpret_cast<float*>(smem + kStages * Shape::kStageBytes);
+  float* scale_ring = reinterpret_cast<float*>(smem + kStages * Shape::kStageBytes);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * Shape::kStageBytes +
                                                    Shape::kScaleBytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full_bar = empty_bar + kStages;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  uint64_t* scale_full_bar = tmem_empty_bar + 2;
+  uint64_t* scale_empty_bar = scale_full_bar + Shape::kScaleSlots;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(scale_empty_bar + Shape::kScaleSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -265,6 +316,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tmem_full_bar[i], 1);
       mbar_init(&tmem_empty_bar[i], kPromoWarps * kCtaGroup);
+    }
+    for (int i = 0; i < Shape::kScaleSlots; ++i) {
+      mbar_init(&scale_full_bar[i], 32);            // every lane of the scale warp
+      mbar_init(&scale_empty_bar[i], kPromoWarps);  // one arrival per promotion warp
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -437,16 +492,77 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
+  } else if (warp == kScaleWarp && !kDump) {
+    // ------------------------------------------------------------ scale staging warp
+    // Copies each group's scale_b columns and scale_a rows into a shared-memory ring, one
+    // group ahead in registers, so that the promotion warps never wait on global memory.
+    constexpr int kColumnsPerLane = BN / 32;
+    uint32_t slot = 0, phase = 0;
+    bool ok = true;
+    for (int tile = worker; tile < total_tiles && ok; tile += workers) {
+      const TileWork work = decode_tile(p, tile);
+      int row0, row_limit;
+      const float* sb_base = p.scale_b;
+      if constexpr (kGrouped) {
+        const int expert = p.tile_expert[work.tm];
+        if (expert < 0) continue;
+        row0 = p.tile_row[work.tm] + static_cast<int>(cta_rank) * Shape::kBM;
+        row_limit = p.expert_offsets[expert + 1];
+        sb_base += static_cast<long long>(expert) * p.sb_expert_stride;
+      } else {
+        row0 = (work.tm * kCtaGroup + static_cast<int>(cta_rank)) * Shape::kBM;
+        row_limit = p.m;
+      }
+      const int n0 = work.tn * BN;
+      float sb_next[kColumnsPerLane], sa_next[4];
+      auto fetch = [&](int g) {
+#pragma unroll
+        for (int i = 0; i < kColumnsPerLane; ++i) {
+          const int col = n0 + lane + 32 * i;
+          sb_next[i] = col < p.n ? sb_base[g * p.sb_sg + col * p.sb_sn] : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = row0 + lane + 32 * i;
+          sa_next[i] = r < row_limit ? p.scale_a[r * p.sa_sm + g * p.sa_sg] : 0.0f;
+        }
+      };
+      fetch(work.group_begin);
+      for (int g = 0; g < work.groups; ++g) {
+        float sb_now[kColumnsPerLane], sa_now[4];
+#pragma unroll
+        for (int i = 0; i < kColumnsPerLane; ++i) sb_now[i] = sb_next[i];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sa_now[i] = sa_next[i];
+        if (g + 1 < work.groups) fetch(work.group_begin + g + 1);
+        const bool got = mbar_test(&scale_empty_bar[slot], phase ^ 1u) ||
+                         mbar_wait(&scale_empty_bar[slot], phase ^ 1u, kSiteScaleEmpty, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          ok = false;
+          break;
+        }
+        float* destination = scale_ring + slot * Shape::kScaleSlotFloats;
+#pragma unroll
+        for (int i = 0; i < kColumnsPerLane; ++i) destination[lane + 32 * i] = sb_now[i];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) destination[BN + lane + 32 * i] = sa_now[i];
+        mbar_arrive(&scale_full_bar[slot]);
+        if (++slot == Shape::kScaleSlots) {
+          slot = 0;
+          phase ^= 1u;
+        }
+      }
+    }
   }
   } else {
     setmaxnreg_inc<Shape::kPromoRegisters>();
     // ------------------------------------------------------------ promotion warps
     const int half = warp >> 2;           // which slice of the BN columns
     const int quarter = warp & 3;         // TMEM lane quarter this warp may read
-    const int tid = threadIdx.x;          // 0..kPromoThreads-1
     const int row_in_cta = quarter * 32 + lane;
     const int col_base = half * kNC;
     uint32_t group_sequence = 0;
+    uint32_t scale_slot = 0, scale_phase = 0;
     bool ok = true;
     [[maybe_unused]] int trace_cursor = 0;
     OutT* c = reinterpret_cast<OutT*>(p.c);
@@ -515,26 +631,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         continue;
       }
-      const int sb_col = n0 + tid;
-      const bool sb_ok = tid < BN && sb_col < p.n;
-
-      float2 acc[kNC / 2];
+      // Fragment layout: this thread owns rows (lane / 4) + 8 * s, s = 0..3, of its warp's 32
+      // rows, and in every 8-column group the two columns 2 * (lane % 4), +1.
+      constexpr int kBlocks = kNC / 32;          // 32-column blocks in this warp's columns
+      constexpr int kPairs = kNC / 8;            // column pairs per owned row
+      float2 acc[4][kPairs];
 #pragma unroll
-      for (int i = 0; i < kNC / 2; ++i) acc[i] = make_float2(0.0f, 0.0f);
-
-      // Stage the first group's column scales; later groups are prefetched one ahead.
-      if (tid < BN) sb_ring[tid] = sb_ok ? sb_base[sb_col * p.sb_sn] : 0.0f;
-      float sa_next = row_ok ? p.scale_a[row * p.sa_sm] : 0.0f;
-      named_barrier_sync(1, kPromoThreads);
+      for (int r = 0; r < 4; ++r) {
+#pragma unroll
+        for (int i = 0; i < kPairs; ++i) acc[r][i] = make_float2(0.0f, 0.0f);
+      }
       static_assert(!kDump || kCtaGroup == 1, "split-K dump runs on single CTAs");
+      const int fragment_row = lane >> 2;
+      const int fragment_col = 2 * (lane & 3);
 
       for (int g = 0; g < groups; ++g, ++group_sequence) {
-        const float sa = sa_next;
-        float sb_next = 0.0f;
-        if (g + 1 < groups) {
-          if (sb_ok) sb_next = sb_base[(g + 1) * p.sb_sg + sb_col * p.sb_sn];
-          if (row_ok) sa_next = p.scale_a[row * p.sa_sm + (g + 1) * p.sa_sg];
+        // This group's scales, staged by the scale warp.
+        if (ok && !mbar_test(&scale_full_bar[scale_slot], scale_phase) &&
+            !mbar_wait(&scale_full_bar[scale_slot], scale_phase, kSiteScaleFull, abort_flag)) {
+          ok = false;
         }
+        const float* scale_slot_base = scale_ring + scale_slot * Shape::kScaleSlotFloats;
+        float sa[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) sa[r] = scale_slot_base[BN + quarter * 32 + fragment_row + 8 * r];
         const uint32_t buffer = group_sequence & 1u;
         if (ok && !mbar_wait(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
                              kSiteEpilogueTmemFull, abort_flag)) {
@@ -542,20 +662,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         tcgen05_fence_after();
         if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 1);
-        const float* sb_slot = sb_ring + (g & 1) * BN + col_base;
-        const uint32_t taddr =
+        const float* sb_columns = scale_slot_base + col_base + fragment_col;
+        const uint32_t taddr_low =
             tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN + col_base;
-        // Two register buffers: the load of chunk c+1 is in flight while chunk c is promoted.
-        uint32_t partial_a[kDW], partial_b[kDW];
-        if (ok) tmem_ld_columns<kDW>(taddr, partial_a);
+        const uint32_t taddr_high = taddr_low + (16u << 16);
+        // Fragments alternate between the two 16-row halves of each 32-column block; the load
+        // of the next fragment is in flight while the current one is promoted.
+        uint32_t partial_a[16], partial_b[16];
+        float2 sb[4];
+        if (ok) tmem_ld_16x256b_x4(taddr_low, partial_a);
 #pragma unroll
-        for (int chunk = 0; chunk < kNC / kDW; ++chunk) {
+        for (int fragment = 0; fragment < 2 * kBlocks; ++fragment) {
           if (!ok) break;
+          const int block = fragment >> 1;
+          const int high_half = fragment & 1;
+          if (!high_half) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              sb[i] = *reinterpret_cast<const float2*>(sb_columns + block * 32 + 8 * i);
+          }
           tmem_ld_wait();
-          if (chunk == 0 && threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 4);
-          if (chunk + 1 < kNC / kDW) {
-            if (chunk & 1) tmem_ld_columns<kDW>(taddr + (chunk + 1) * kDW, partial_a);
-            else tmem_ld_columns<kDW>(taddr + (chunk + 1) * kDW, partial_b);
+          if (fragment == 0 && threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 4);
+          if (fragment + 1 < 2 * kBlocks) {
+            const uint32_t next = ((fragment + 1) & 1 ? taddr_high : taddr_low) +
+                                  ((fragment + 1) >> 1) * 32;
+            if (fragment & 1) tmem_ld_16x256b_x4(next, partial_a);
+            else tmem_ld_16x256b_x4(next, partial_b);
           } else {
             // All of this warp's TMEM reads for the buffer are done: hand it back.
             tcgen05_fence_before();
@@ -565,26 +697,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               else mbar_arrive_cluster(&tmem_empty_bar[buffer], 0);
             }
           }
-          if (chunk & 1) promote<kDW>(partial_b, sa, sb_slot + chunk * kDW, acc + chunk * kDW / 2);
-          else promote<kDW>(partial_a, sa, sb_slot + chunk * kDW, acc + chunk * kDW / 2);
+          if (fragment & 1) {
+            promote_fragment(partial_b, sa[2], sa[3], sb, &acc[2][block * 4], &acc[3][block * 4]);
+          } else {
+            promote_fragment(partial_a, sa[0], sa[1], sb, &acc[0][block * 4], &acc[1][block * 4]);
+          }
         }
         if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 2);
-        if (tid < BN) sb_ring[((g + 1) & 1) * BN + tid] = sb_next;
-        named_barrier_sync(1, kPromoThreads);
+        // Every lane has consumed the slot's values (they fed the arithmetic above).
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&scale_empty_bar[scale_slot]);
+        if (++scale_slot == Shape::kScaleSlots) {
+          scale_slot = 0;
+          scale_phase ^= 1u;
+        }
         if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 3);
       }
-      if (row_ok && ok) {
-        OutT* c_row = c + static_cast<long long>(row) * p.ldc + n0 + col_base;
-        const int remaining = p.n - (n0 + col_base);
+      if (ok) {
+        const int first_row = row - row_in_cta + quarter * 32 + fragment_row;
+        const int first_col = n0 + col_base + fragment_col;
+        const bool aligned = p.c_vector_ok != 0;
 #pragma unroll
-        for (int j = 0; j < kNC; j += 8) {
-          const float values[8] = {acc[j / 2].x,     acc[j / 2].y,     acc[j / 2 + 1].x,
-                                   acc[j / 2 + 1].y, acc[j / 2 + 2].x, acc[j / 2 + 2].y,
-                                   acc[j / 2 + 3].x, acc[j / 2 + 3].y};
-          if (j + 8 <= remaining && p.c_vector_ok) {
-            store_row_vector8<OutT>(c_row + j, values);
-          } else if (j < remaining) {
-            store_row_chunk<OutT>(c_row + j, values, min(8, remaining - j));
+        for (int r = 0; r < 4; ++r) {
+          const int out_row = first_row + 8 * r;
+          if (out_row < row_limit) {
+            OutT* c_row = c + static_cast<long long>(out_row) * p.ldc;
+#pragma unroll
+            for (int i = 0; i < kPairs; ++i) {
+              const int col = first_col + (i >> 2) * 32 + (i & 3) * 8;
+              if (col < p.n) store_pair<OutT>(c_row + col, acc[r][i], col + 1 < p.n, aligned);
+            }
           }
         }
       }
