@@ -223,6 +223,7 @@ static int launch_gemm_tc(const GemmArgs& g, int variant, cudaStream_t stream) {
   p.ldc = g.ldc;
   p.group_size = g.group_size;
   p.k_splits = 1;
+  p.band_rows = 16;
   p.tiles_m = (g.m + (pair ? 255 : 127)) / (pair ? 256 : 128);
   p.tiles_n = (g.n + bn - 1) / bn;
   const int out_bytes = g.out_dtype == GG_OUT_FP32 ? 4 : 2;
@@ -253,6 +254,7 @@ static int launch_gemm_splitk(const GemmArgs& g, void* workspace, size_t workspa
   p.m = g.m; p.n = g.n; p.k = g.k;
   p.group_size = g.group_size;
   p.tiles_m = 1;
+  p.band_rows = 8;
   p.tiles_n = (g.n + 255) / 256;
   p.k_splits = plan.splits;
   p.groups_per_split = plan.groups_per_split;
@@ -654,6 +656,7 @@ int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_
     p.ldc = hidden;
     p.group_size = 256;
     p.k_splits = 1;
+    p.band_rows = 8;
     p.tiles_m = tile_capacity;
     p.tiles_n = (hidden + bn - 1) / bn;
     p.c_vector_ok = 1;

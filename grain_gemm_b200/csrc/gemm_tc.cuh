@@ -54,6 +54,7 @@ struct GemmTcParams {
   // Split-K dump mode: the K groups are divided over k_splits work items per output tile and
   // the INT32 group dots go to partials[Q][M][N] instead of being promoted (a second kernel
   // then folds them in group order).  k_splits == 1 and partials == null otherwise.
+  int band_rows;               // row tiles per scheduling band
   int k_splits;
   int groups_per_split;
   int* partials;
@@ -105,12 +106,12 @@ struct GemmTcShape {
 };
 
 __device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tiles_n, int& tm,
-                                                 int& tn) {
-  // Bands of eight row tiles: consecutive CTAs share B columns and a few A rows in L2.
-  const int band_size = 8 * tiles_n;
+                                                 int& tn, int band_rows = 8) {
+  // Bands of row tiles: consecutive CTAs share B columns and a few A rows in L2.
+  const int band_size = band_rows * tiles_n;
   const int band = tile / band_size;
-  const int first_m = band * 8;
-  const int band_m = min(tiles_m - first_m, 8);
+  const int first_m = band * band_rows;
+  const int band_m = min(tiles_m - first_m, band_rows);
   const int local = tile - band * band_size;
   tm = first_m + local % band_m;
   tn = local / band_m;
@@ -124,7 +125,7 @@ __device__ __forceinline__ TileWork decode_tile(const GemmTcParams& p, int tile)
     split = tile / per_split;
     tile -= split * per_split;
   }
-  tile_coordinates(tile, p.tiles_m, p.tiles_n, w.tm, w.tn);
+  tile_coordinates(tile, p.tiles_m, p.tiles_n, w.tm, w.tn, p.band_rows);
   const int total_groups = (p.k + p.group_size - 1) / p.group_size;
   w.group_begin = split * p.groups_per_split;
   const int group_end = p.k_splits > 1 ? min(total_groups, w.group_begin + p.groups_per_split)
@@ -202,11 +203,7 @@ __device__ __forceinline__ void promote(const uint32_t (&partial)[kWidth], float
                                         const float* __restrict__ sb_smem, float2* acc) {
 #pragma unroll
   for (int j = 0; j < kWidth; j += 4) {
-#ifdef GG_EXPERIMENT_NO_SB
-    const float4 sb = make_float4(1.0f, 2.0f, 3.0f, 4.0f);
-#else
     const float4 sb = *reinterpret_cast<const float4*>(sb_smem + j);
-#endif
 #ifdef GG_CONVERT_I2F
     const float2 p01 = make_float2(__int2float_rn(static_cast<int>(partial[j + 0])),
                                    __int2float_rn(static_cast<int>(partial[j + 1])));
@@ -377,6 +374,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tma_load_2d_pair(a_dst, &map_a, &full_bar[stage], x, row_a);
             tma_load_2d_pair(b_dst, &map_b, &full_bar[stage], x, row_b);
           }
+          GG_TRACE_EVENT(0, trace_cursor, 5);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -429,6 +427,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             umma_i8<kCtaGroup>(tmem_d, a_low + 2, b_low + 2, idesc, 1u);
             umma_i8<kCtaGroup>(tmem_d, a_low + 4, b_low + 4, idesc, 1u);
             umma_i8<kCtaGroup>(tmem_d, a_low + 6, b_low + 6, idesc, 1u);
+            GG_TRACE_EVENT(1, trace_cursor, 6);
             if constexpr (kCtaGroup == 1) umma_commit(&empty_bar[stage]);
             else umma_commit_pair(&empty_bar[stage], 3);
             if (!group_start) {
