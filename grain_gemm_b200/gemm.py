@@ -111,10 +111,34 @@ def get_kernel_config(a, b, *, group_size=256, output_dtype=torch.bfloat16,
                 tensor_cores=name.startswith("tc"))
 
 
+_REPACK_MIN_OPS = 1 << 32
+
+
+def _tensor_core_operands(a, b):
+    """Operands in the layout the tensor-core path reads (K contiguous, 16-byte aligned rows).
+
+    Any positive-stride view is accepted by the CUDA-core kernel, but that kernel is two orders
+    of magnitude slower on large problems.  For those, an operand whose K direction is not
+    contiguous (a row-major ``[K, N]`` B, a transposed A) or whose rows are not 16-byte aligned
+    is copied once into K-contiguous storage; the arithmetic and the result do not change.
+    """
+    m, k = a.shape
+    n = b.shape[1]
+    if 2 * m * n * k < _REPACK_MIN_OPS or k % 16:
+        return a, b
+    if a.stride(1) != 1 or a.stride(0) % 16 or a.data_ptr() % 16:
+        a = a.contiguous()
+    if b.stride(0) != 1 or b.stride(1) % 16 or b.data_ptr() % 16:
+        b = b.t().contiguous().t()
+    return a, b
+
+
 def launch(a, b, scale_a, scale_b, out, group_size, variant="auto"):
     """Launch the GEMM on torch's current stream (arguments already validated)."""
     m, k = a.shape
     n = b.shape[1]
+    if variant == "auto":
+        a, b = _tensor_core_operands(a, b)
     lib = _loader.library()
     workspace, workspace_bytes = None, 0
     if variant in ("auto", "tc_splitk"):

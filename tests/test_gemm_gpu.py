@@ -217,6 +217,22 @@ def test_full_size_linearity_property(gg):
     assert torch.equal(out[rows][:, cols].cpu(), expected)
 
 
+def test_large_row_major_b_is_repacked_for_the_tensor_cores(gg):
+    """A contiguous [K, N] B (N fastest) must not fall off a performance cliff: it is copied
+    to K-contiguous storage once and gives the same bits as the Linear-format view."""
+    m, n, k = 512, 2048, 4096
+    a, b, sa, sb = linear_case(m, n, k, 256, seed=21)
+    expected = oracle.int8_gemm(a, b, sa, sb, 256, torch.bfloat16)
+    row_major = b.contiguous().cuda()
+    assert row_major.stride() == (n, 1)
+    out = gg.int8_gemm(a.cuda(), row_major, sa.cuda(), sb.cuda(), group_size=256)
+    assert torch.equal(out.cpu(), expected)
+    column_major_a = a.t().contiguous().t().cuda()
+    assert column_major_a.stride() == (1, m)
+    out = gg.int8_gemm(column_major_a, b.cuda(), sa.cuda(), sb.cuda(), group_size=256)
+    assert torch.equal(out.cpu(), expected)
+
+
 def test_zero_sized_and_config_description(gg):
     a = torch.zeros((0, 64), dtype=torch.int8, device="cuda")
     b = torch.zeros((64, 8), dtype=torch.int8, device="cuda")
