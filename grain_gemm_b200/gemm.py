@@ -99,8 +99,22 @@ def get_kernel_config(a, b, *, group_size=256, output_dtype=torch.bfloat16,
     """
     _check_backend(backend)
     capability = torch.cuda.get_device_capability(a.device)
+    m, k = a.shape
+    n = b.shape[1]
+    repack_a, repack_b = _repack_plan(a, b)
     with torch.cuda.device(a.device):
-        variant = _select(a, b, None, group_size, output_dtype)
+        if repack_a or repack_b:
+            # Describe the launch on the repacked (K-contiguous, aligned) operands.
+            aligned = _loader._VOID(256)
+            a_strides = (k, 1) if repack_a else a.stride()
+            b_strides = (1, k) if repack_b else b.stride()
+            variant = _loader.library().gg_int8_gemm_select(
+                aligned if repack_a else _loader.pointer(a),
+                aligned if repack_b else _loader.pointer(b), None, m, n, k,
+                a_strides[0], a_strides[1], b_strides[0], b_strides[1], n, group_size,
+                _loader.OUT_DTYPE[output_dtype])
+        else:
+            variant = _select(a, b, None, group_size, output_dtype)
     name = _loader.VARIANT_NAMES[variant]
     pair = name.startswith("tc_pair")
     block_n = (256 if name == "tc_splitk" else int(name.split("_n", 1)[1].split("_")[0])
@@ -108,10 +122,20 @@ def get_kernel_config(a, b, *, group_size=256, output_dtype=torch.bfloat16,
     return dict(policy="sm100_native", compute_capability=list(capability), backend="cuda",
                 variant=name, block_m=(256 if pair else 128) if name.startswith("tc") else 32,
                 block_n=block_n, cta_group=2 if pair else 1,
-                tensor_cores=name.startswith("tc"))
+                tensor_cores=name.startswith("tc"), repacked_a=repack_a, repacked_b=repack_b)
 
 
 _REPACK_MIN_OPS = 1 << 32
+
+
+def _repack_plan(a, b):
+    """(repack A?, repack B?) for the rule described in ``_tensor_core_operands``."""
+    m, k = a.shape
+    n = b.shape[1]
+    if 2 * m * n * k < _REPACK_MIN_OPS or k % 16:
+        return False, False
+    return (a.stride(1) != 1 or a.stride(0) % 16 != 0 or a.data_ptr() % 16 != 0,
+            b.stride(0) != 1 or b.stride(1) % 16 != 0 or b.data_ptr() % 16 != 0)
 
 
 def _tensor_core_operands(a, b):
@@ -122,13 +146,10 @@ def _tensor_core_operands(a, b):
     contiguous (a row-major ``[K, N]`` B, a transposed A) or whose rows are not 16-byte aligned
     is copied once into K-contiguous storage; the arithmetic and the result do not change.
     """
-    m, k = a.shape
-    n = b.shape[1]
-    if 2 * m * n * k < _REPACK_MIN_OPS or k % 16:
-        return a, b
-    if a.stride(1) != 1 or a.stride(0) % 16 or a.data_ptr() % 16:
+    repack_a, repack_b = _repack_plan(a, b)
+    if repack_a:
         a = a.contiguous()
-    if b.stride(0) != 1 or b.stride(1) % 16 or b.data_ptr() % 16:
+    if repack_b:
         b = b.t().contiguous().t()
     return a, b
 

@@ -243,7 +243,9 @@ def test_zero_sized_and_config_description(gg):
     assert config["backend"] == "cuda" and config["policy"] == "sm100_native"
     assert config["compute_capability"] == [10, 0] and config["tensor_cores"]
     config = gg.get_kernel_config(a, b.contiguous(), group_size=256)
-    assert config["variant"] == "simt"
+    assert config["tensor_cores"] and config["repacked_b"] and not config["repacked_a"]
+    config = gg.get_kernel_config(a[:16, :64], b[:64, :24].contiguous(), group_size=32)
+    assert config["variant"] == "simt" and not config["repacked_b"]
     with pytest.raises(ValueError, match="stride"):
         gg.int8_gemm(a[:1].expand(8192, 512), b, torch.ones((8192, 2), device="cuda"),
                      torch.ones((2, 8192), device="cuda"))
