@@ -345,14 +345,32 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
         float acc[64];
         float amax = 0.0f;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const float gate_split = (c & 1) ? acc2[c / 2].y : acc2[c / 2].x;
-          const float up_split = (c & 1) ? acc2[32 + c / 2].y : acc2[32 + c / 2].x;
-          const float gate = round_through<RoundT>(p.interleaved ? acc2[c].x : gate_split);
-          const float up = round_through<RoundT>(p.interleaved ? acc2[c].y : up_split);
-          const float h = swiglu_value(gate, up);
-          acc[c] = h;
-          amax = fmaxf(amax, fabsf(h));
+        for (int c0 = 0; c0 < 64; c0 += 8) {
+          float gate[8], up[8], denominator[8];
+          bool safe = true;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j;
+            const float gate_split = (c & 1) ? acc2[c / 2].y : acc2[c / 2].x;
+            const float up_split = (c & 1) ? acc2[32 + c / 2].y : acc2[32 + c / 2].x;
+            gate[j] = round_through<RoundT>(p.interleaved ? acc2[c].x : gate_split);
+            up[j] = round_through<RoundT>(p.interleaved ? acc2[c].y : up_split);
+            denominator[j] = __fadd_rn(1.0f, expf(-gate[j]));
+            safe = safe && swiglu_division_is_safe(gate[j], denominator[j]);
+          }
+          if (safe) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float y = reciprocal_by_fma(denominator[j]);
+              acc[c0 + j] = __fmul_rn(divide_by_fma(gate[j], denominator[j], y), up[j]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              acc[c0 + j] = __fmul_rn(__fdiv_rn(gate[j], denominator[j]), up[j]);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(acc[c0 + j]));
         }
         amax_part[(sub * 2 + half) * 128 + row_in_tile] = amax;
         if (sub == 0) {
@@ -369,29 +387,38 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
           const float scale = quantize_scale(row_max);
           if (row_ok && ok) {
             int8_t* q_row = p.q + static_cast<long long>(row) * p.intermediate + jg * 256;
+            const bool by_fma = quantize_division_is_safe(row_max);
+            const float y = __frcp_rn(scale);
 #pragma unroll
             for (int piece = 0; piece < 2; ++piece) {
               // piece 0: parked first sub-tile (channels half*64..), piece 1: registers.
               uint4* dst = reinterpret_cast<uint4*>(q_row + piece * 128 + half * 64);
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
-                uint32_t words[4];
+                float h16[16];
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                   const int c = v * 16 + w * 4;
-                  float h4[4];
                   if (piece == 0) {
                     const float4 parked = *reinterpret_cast<const float4*>(stash_row + c);
-                    h4[0] = parked.x; h4[1] = parked.y; h4[2] = parked.z; h4[3] = parked.w;
+                    h16[w * 4] = parked.x; h16[w * 4 + 1] = parked.y;
+                    h16[w * 4 + 2] = parked.z; h16[w * 4 + 3] = parked.w;
                   } else {
-                    h4[0] = acc[c]; h4[1] = acc[c + 1]; h4[2] = acc[c + 2]; h4[3] = acc[c + 3];
-                  }
-                  uint32_t packed = 0;
 #pragma unroll
-                  for (int b = 0; b < 4; ++b) {
-                    packed |= (static_cast<uint32_t>(quantize_value(h4[b], scale)) & 0xffu) << (8 * b);
+                    for (int b = 0; b < 4; ++b) h16[w * 4 + b] = acc[c + b];
                   }
-                  words[w] = packed;
+                }
+                uint32_t words[4] = {0u, 0u, 0u, 0u};
+                if (by_fma) {
+#pragma unroll
+                  for (int b = 0; b < 16; ++b)
+                    words[b / 4] |= (static_cast<uint32_t>(quantize_value_by_fma(h16[b], scale, y)) & 0xffu)
+                                    << (8 * (b % 4));
+                } else {
+#pragma unroll
+                  for (int b = 0; b < 16; ++b)
+                    words[b / 4] |= (static_cast<uint32_t>(quantize_value(h16[b], scale)) & 0xffu)
+                                    << (8 * (b % 4));
                 }
                 dst[v] = make_uint4(words[0], words[1], words[2], words[3]);
               }

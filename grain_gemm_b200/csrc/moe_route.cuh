@@ -223,6 +223,44 @@ __device__ __forceinline__ int quantize_value(float h, float scale) {
   return static_cast<int>(fminf(fmaxf(rounded, -127.0f), 127.0f));
 }
 
+// The library division carries a branch to a slow path, which keeps the compiler from
+// interleaving the long dependent chains of many divisions.  The fused Gate/Up epilogue
+// therefore divides with the classical FMA sequence, which is branch-free and, by
+// Markstein's theorems, still correctly rounded:
+//   * y0 = rcp.approx(d) is within 1 ulp, so y = fma(fma(-d, y0, 1), y0, y0) is the
+//     correctly rounded reciprocal unless d's significand is all ones;
+//   * with y = RN(1/d), q within 1 ulp of n/d and r = fma(-d, q, n) exact,
+//     fma(r, y, q) is the correctly rounded quotient.
+// Both need every intermediate to stay normal; callers test the operand ranges and fall
+// back to the library division outside them, so results always equal __fdiv_rn (a zero
+// numerator may lose its sign, which neither the scale nor the INT8 code can show).
+__device__ __forceinline__ float reciprocal_by_fma(float d) {
+  float y0;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(y0) : "f"(d));
+  return __fmaf_rn(__fmaf_rn(-d, y0, 1.0f), y0, y0);
+}
+__device__ __forceinline__ float divide_by_fma(float n, float d, float y) {
+  float q = __fmul_rn(n, y);
+  q = __fmaf_rn(__fmaf_rn(-d, q, n), y, q);  // now within 1 ulp
+  return __fmaf_rn(__fmaf_rn(-d, q, n), y, q);
+}
+// SwiGLU operands for which the sequence is exact: |gate| <= 64 keeps the denominator
+// 1 + exp(-gate) within [1, 2^93) and the quotient far from underflow.
+__device__ __forceinline__ bool swiglu_division_is_safe(float gate, float denominator) {
+  const float magnitude = fabsf(gate);
+  const bool numerator_ok = magnitude <= 64.0f && (magnitude >= 0x1p-60f || magnitude == 0.0f);
+  return numerator_ok && (__float_as_uint(denominator) & 0x7fffffu) != 0x7fffffu;
+}
+// Row scales for which h / scale may use the sequence with y = __frcp_rn(scale): quotients
+// of magnitude >= 1/4 then have normal residuals, and smaller ones round to 0 either way.
+__device__ __forceinline__ bool quantize_division_is_safe(float row_max) {
+  return row_max < 1.0e30f;  // also false for NaN and infinity
+}
+__device__ __forceinline__ int quantize_value_by_fma(float h, float scale, float y) {
+  const float rounded = nearbyintf(divide_by_fma(h, scale, y));
+  return static_cast<int>(fminf(fmaxf(rounded, -127.0f), 127.0f));
+}
+
 // Stand-alone SwiGLU + G256 requantisation over a [rows, 2I] gate/up matrix (the unfused
 // path).  One warp per (row, 256-channel group); rows at or beyond *valid_rows get q = 0 and
 // scale = 1e-12/127.

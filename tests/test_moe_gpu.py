@@ -216,6 +216,33 @@ def test_unmasked_invalid_ids_raise(moe):
         moe.moe_ffn(**to_cuda(case))
 
 
+@pytest.mark.parametrize("layout", ["split", "interleaved"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_gate_up_equals_unfused_bits(moe, layout, dtype):
+    """The fused epilogue divides with an FMA sequence, the stand-alone SwiGLU kernel with
+    the library division; codes and scales must agree bit for bit, also for rows whose gate
+    values are zero, huge (exp overflows, quotient -0) or far beyond the FMA sequence's range."""
+    case = make_case(1500, 512, 1024, 6, 2, layout=layout, dtype=dtype, seed=11)
+    case["scale_x"][0:40] = 0.0          # gate = up = 0
+    case["scale_x"][40:80] *= 300.0      # |gate| in the hundreds: exp(-gate) overflows
+    case["scale_x"][80:120] *= 1.0e-30   # tiny numerators
+    case["scale_x"][120:160] *= 30.0     # around the range test of the FMA sequence
+    dev = to_cuda(case)
+    experts = case["w_gate_up"].shape[0]
+    w1 = dev["w_gate_up"].transpose(-2, -1)
+    results = []
+    for tile_rows in (128, 32):
+        routes = moe.prepare_routes(dev["topk_ids"], experts, None, tile_rows=tile_rows)
+        qh, sh = moe.gate_up_swiglu_quantize(dev["hidden_states"], dev["scale_x"], w1,
+                                             dev["scale_gate_up"], routes, output_dtype=dtype,
+                                             gate_up_layout=layout)
+        valid = int(routes.offsets[-1])
+        results.append((qh[:valid].cpu(), sh[:valid].cpu()))
+    assert torch.equal(results[0][0], results[1][0])
+    assert torch.equal(results[0][1], results[1][1])
+    assert results[0][0].abs().max() == 127
+
+
 def test_interleaved_equals_split_bits(moe):
     split = make_case(200, 512, 512, 6, 2, layout="split", seed=5)
     inter = make_case(200, 512, 512, 6, 2, layout="interleaved", seed=5)
