@@ -3,7 +3,8 @@
 Configurations follow BASELINE.json: ``decode_small`` (T=512, H=2048, I=768, E=128, top-8,
 split), ``interleaved_decode`` / ``interleaved_prefill`` (H=4096, I=14336, E=8, top-2, T=16 /
 4096, one expert biased, interleaved gate/up) and ``large`` (T=16384, H=7168, I=2048, E=256,
-top-8), the expert-parallel case.  All tensors are generated on the device from seeds, so that
+top-8), the expert-parallel case, and ``large_rank_share`` (T=2048, E=32 of the same shape: the
+experts and rows one rank of eight holds, small enough to profile).  All tensors are generated on the device from seeds, so that
 every expert-parallel rank can materialise only its own experts: expert ``e`` always gets the
 same weights whatever the world size.
 """
@@ -21,6 +22,8 @@ CONFIGS = {
                                 layout="interleaved", biased=True),
     "large": dict(tokens=16384, hidden=7168, inter=2048, experts=256, top_k=8,
                   layout="split", biased=False),
+    "large_rank_share": dict(tokens=2048, hidden=7168, inter=2048, experts=32, top_k=8,
+                             layout="split", biased=False),
 }
 
 

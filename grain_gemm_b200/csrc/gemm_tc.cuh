@@ -271,6 +271,35 @@ __device__ __forceinline__ void store_pair(OutT* dst, float2 v, bool both, bool 
   }
 }
 
+// Two outputs as one 32-bit word, the first in the low half.
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack_pair(float2 v) {
+  if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+    const __nv_bfloat162 packed = __floats2bfloat162_rn(v.x, v.y);
+    return *reinterpret_cast<const uint32_t*>(&packed);
+  } else {
+    const __half2 packed = __floats2half2_rn(v.x, v.y);
+    return *reinterpret_cast<const uint32_t*>(&packed);
+  }
+}
+
+// 4x4 transpose inside every quad of lanes: lane q (= lane & 3) enters with its words
+// w[0..3] and leaves with word q of lanes 0, 1, 2, 3 of its quad, in that order.
+__device__ __forceinline__ void quad_transpose(uint32_t (&w)[4], int q) {
+  const bool odd = (q & 1) != 0;
+  uint32_t s0 = odd ? w[0] : w[1];
+  uint32_t s1 = odd ? w[2] : w[3];
+  s0 = __shfl_xor_sync(0xffffffffu, s0, 1);
+  s1 = __shfl_xor_sync(0xffffffffu, s1, 1);
+  if (odd) { w[0] = s0; w[2] = s1; } else { w[1] = s0; w[3] = s1; }
+  const bool upper = (q & 2) != 0;
+  uint32_t t0 = upper ? w[0] : w[2];
+  uint32_t t1 = upper ? w[1] : w[3];
+  t0 = __shfl_xor_sync(0xffffffffu, t0, 2);
+  t1 = __shfl_xor_sync(0xffffffffu, t1, 2);
+  if (upper) { w[0] = t0; w[1] = t1; } else { w[2] = t0; w[3] = t1; }
+}
+
 template <int kCtaGroup, int BN, int kStages, typename OutT, bool kGrouped, int kPromoWarps,
           bool kDump = false, int kARows = 128>
 __global__ void __launch_bounds__((kPromoWarps + 4) * 32, 1)
@@ -338,30 +367,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   setmaxnreg_dec<Shape::kAuxRegisters>();
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      [[maybe_unused]] int trace_cursor = 0;
-      for (int tile = worker; tile < total_tiles && ok; tile += workers) {
-        const TileWork work = decode_tile(p, tile);
-        const int tm = work.tm, tn = work.tn;
-        int row_a, row_b;
-        if constexpr (kGrouped) {
-          const int expert = p.tile_expert[tm];
-          if (expert < 0) continue;
-          row_a = p.tile_row[tm] + static_cast<int>(cta_rank) * Shape::kBM;
-          row_b = expert * static_cast<int>(p.b_rows_per_expert) + tn * BN +
-                  static_cast<int>(cta_rank) * Shape::kBRows;
-        } else {
-          row_a = (tm * kCtaGroup + static_cast<int>(cta_rank)) * Shape::kBM;
-          row_b = tn * BN + static_cast<int>(cta_rank) * Shape::kBRows;
+    // The whole warp walks the ring (see mbar_wait_warp); one elected lane issues the copies.
+    const bool leader = elect_one();
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    [[maybe_unused]] int trace_cursor = 0;
+    for (int tile = worker; tile < total_tiles && ok; tile += workers) {
+      const TileWork work = decode_tile(p, tile);
+      const int tm = work.tm, tn = work.tn;
+      int row_a, row_b;
+      if constexpr (kGrouped) {
+        const int expert = p.tile_expert[tm];
+        if (expert < 0) continue;
+        row_a = p.tile_row[tm] + static_cast<int>(cta_rank) * Shape::kBM;
+        row_b = expert * static_cast<int>(p.b_rows_per_expert) + tn * BN +
+                static_cast<int>(cta_rank) * Shape::kBRows;
+      } else {
+        row_a = (tm * kCtaGroup + static_cast<int>(cta_rank)) * Shape::kBM;
+        row_b = tn * BN + static_cast<int>(cta_rank) * Shape::kBRows;
+      }
+      for (int slab = 0, x = work.k_begin; slab < work.slabs; ++slab, x += Shape::kBK) {
+        if (!mbar_wait_warp(&empty_bar[stage], phase ^ 1u, kSiteProducerEmpty, abort_flag)) {
+          ok = false;
+          break;
         }
-        for (int slab = 0, x = work.k_begin; slab < work.slabs; ++slab, x += Shape::kBK) {
-          if (!mbar_test(&empty_bar[stage], phase ^ 1u) &&
-              !mbar_wait(&empty_bar[stage], phase ^ 1u, kSiteProducerEmpty, abort_flag)) {
-            ok = false;
-            break;
-          }
+        if (leader) {
           GG_TRACE_EVENT(0, trace_cursor, 1);
           uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
           uint8_t* b_dst = a_dst + Shape::kABytes;
@@ -375,18 +405,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tma_load_2d_pair(b_dst, &map_b, &full_bar[stage], x, row_b);
           }
           GG_TRACE_EVENT(0, trace_cursor, 5);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+        }
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
-    // One thread issues every MMA; the loop body is kept to a handful of instructions per
-    // MMA (descriptor low words advance by constants, ring positions are running counters).
-    if (cta_rank == 0 && lane == 0) {
+    // The warp of the pair's leader CTA walks the loop converged; one elected lane issues every
+    // MMA and commit.  (A loop run by a single lane of a diverged warp has to move each
+    // descriptor into uniform registers per instruction and issues about a third slower.)
+    if (cta_rank == 0) {
+      const bool leader = elect_one();
       constexpr uint32_t idesc = make_idesc_i8(Shape::kBM * kCtaGroup, BN);
       const uint32_t a_low_base = smem_desc_low(smem_u32(stage_base));
       uint32_t stage = 0, phase = 0;                 // shared-memory ring position
@@ -401,39 +433,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (work.whole_g256) {
           // G = 256 with whole groups: two slabs per group, no per-MMA bookkeeping.
-          for (int slab = 0; slab < work.slabs && ok; ++slab) {
-            if (!mbar_test(&full_bar[stage], phase) &&
-                !mbar_wait(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
+          for (int slab = 0; slab < work.slabs; ++slab) {
+            if (!mbar_wait_warp(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
               ok = false;
               break;
             }
             tcgen05_fence_after();
-            GG_TRACE_EVENT(1, trace_cursor, 1);
+            if (leader) GG_TRACE_EVENT(1, trace_cursor, 1);
             const bool group_start = (slab & 1) == 0;
             if (group_start) {
-              if (!mbar_test(&tmem_empty_bar[buffer], empty_parity) &&
-                  !mbar_wait(&tmem_empty_bar[buffer], empty_parity, kSiteMmaTmemEmpty,
-                             abort_flag)) {
+              if (!mbar_wait_warp(&tmem_empty_bar[buffer], empty_parity, kSiteMmaTmemEmpty,
+                                  abort_flag)) {
                 ok = false;
                 break;
               }
               tcgen05_fence_after();
-              GG_TRACE_EVENT(1, trace_cursor, 2);
+              if (leader) GG_TRACE_EVENT(1, trace_cursor, 2);
             }
             const uint32_t a_low = a_low_base + stage * (Shape::kStageBytes >> 4);
             const uint32_t b_low = a_low + (Shape::kABytes >> 4);
             const uint32_t tmem_d = tmem_base + buffer * BN;
-            umma_i8<kCtaGroup>(tmem_d, a_low, b_low, idesc, group_start ? 0u : 1u);
-            umma_i8<kCtaGroup>(tmem_d, a_low + 2, b_low + 2, idesc, 1u);
-            umma_i8<kCtaGroup>(tmem_d, a_low + 4, b_low + 4, idesc, 1u);
-            umma_i8<kCtaGroup>(tmem_d, a_low + 6, b_low + 6, idesc, 1u);
-            GG_TRACE_EVENT(1, trace_cursor, 6);
-            if constexpr (kCtaGroup == 1) umma_commit(&empty_bar[stage]);
-            else umma_commit_pair(&empty_bar[stage], 3);
+            if (leader) {
+              umma_i8<kCtaGroup>(tmem_d, a_low, b_low, idesc, group_start ? 0u : 1u);
+              umma_i8<kCtaGroup>(tmem_d, a_low + 2, b_low + 2, idesc, 1u);
+              umma_i8<kCtaGroup>(tmem_d, a_low + 4, b_low + 4, idesc, 1u);
+              umma_i8<kCtaGroup>(tmem_d, a_low + 6, b_low + 6, idesc, 1u);
+              GG_TRACE_EVENT(1, trace_cursor, 6);
+              if constexpr (kCtaGroup == 1) umma_commit(&empty_bar[stage]);
+              else umma_commit_pair(&empty_bar[stage], 3);
+              if (!group_start) {
+                if constexpr (kCtaGroup == 1) umma_commit(&tmem_full_bar[buffer]);
+                else umma_commit_pair(&tmem_full_bar[buffer], 3);
+                GG_TRACE_EVENT(1, trace_cursor, 3);
+              }
+            }
             if (!group_start) {
-              if constexpr (kCtaGroup == 1) umma_commit(&tmem_full_bar[buffer]);
-              else umma_commit_pair(&tmem_full_bar[buffer], 3);
-              GG_TRACE_EVENT(1, trace_cursor, 3);
               buffer ^= 1u;
               if (buffer == 0) empty_parity ^= 1u;
             }
@@ -446,44 +480,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         int remaining = work.ksteps;
         for (int slab = 0; slab < work.slabs && ok; ++slab) {
-          if (!mbar_test(&full_bar[stage], phase) &&
-              !mbar_wait(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
+          if (!mbar_wait_warp(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
             ok = false;
             break;
           }
           tcgen05_fence_after();
-          GG_TRACE_EVENT(1, trace_cursor, 1);
+          if (leader) GG_TRACE_EVENT(1, trace_cursor, 1);
           const uint32_t a_low = a_low_base + stage * (Shape::kStageBytes >> 4);
           const uint32_t b_low = a_low + (Shape::kABytes >> 4);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             if (remaining > 0) {
               if (step == 0) {
-                if (!mbar_test(&tmem_empty_bar[buffer], empty_parity) &&
-                    !mbar_wait(&tmem_empty_bar[buffer], empty_parity, kSiteMmaTmemEmpty,
-                               abort_flag)) {
+                if (!mbar_wait_warp(&tmem_empty_bar[buffer], empty_parity, kSiteMmaTmemEmpty,
+                                    abort_flag)) {
                   ok = false;
                   break;
                 }
                 tcgen05_fence_after();
-                GG_TRACE_EVENT(1, trace_cursor, 2);
+                if (leader) GG_TRACE_EVENT(1, trace_cursor, 2);
               }
-              umma_i8<kCtaGroup>(tmem_base + buffer * BN, a_low + 2 * j, b_low + 2 * j, idesc,
-                                 step != 0 ? 1u : 0u);
+              if (leader) {
+                umma_i8<kCtaGroup>(tmem_base + buffer * BN, a_low + 2 * j, b_low + 2 * j, idesc,
+                                   step != 0 ? 1u : 0u);
+              }
               ++step;
               --remaining;
               if (step == steps_per_group || remaining == 0) {
-                if constexpr (kCtaGroup == 1) umma_commit(&tmem_full_bar[buffer]);
-                else umma_commit_pair(&tmem_full_bar[buffer], 3);
-                GG_TRACE_EVENT(1, trace_cursor, 3);
+                if (leader) {
+                  if constexpr (kCtaGroup == 1) umma_commit(&tmem_full_bar[buffer]);
+                  else umma_commit_pair(&tmem_full_bar[buffer], 3);
+                  GG_TRACE_EVENT(1, trace_cursor, 3);
+                }
                 step = 0;
                 buffer ^= 1u;
                 if (buffer == 0) empty_parity ^= 1u;
               }
             }
           }
-          if constexpr (kCtaGroup == 1) umma_commit(&empty_bar[stage]);
-          else umma_commit_pair(&empty_bar[stage], 3);
+          if (leader && ok) {
+            if constexpr (kCtaGroup == 1) umma_commit(&empty_bar[stage]);
+            else umma_commit_pair(&empty_bar[stage], 3);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -712,19 +750,62 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 3);
       }
-      if (ok) {
+      // The fragment layout leaves each lane with column pairs 8 apart.  A 4x4 exchange inside
+      // every quad gives lane q the eight consecutive columns 8q..8q+7 of each 32-column
+      // block, so that a row leaves as 16-byte stores (a quarter of the store instructions and
+      // of the memory-pipe wavefronts of pair stores).
+      if (__all_sync(0xffffffffu, ok)) {
+        const int quad = lane & 3;
         const int first_row = row - row_in_cta + quarter * 32 + fragment_row;
-        const int first_col = n0 + col_base + fragment_col;
         const bool aligned = p.c_vector_ok != 0;
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           const int out_row = first_row + 8 * r;
-          if (out_row < row_limit) {
-            OutT* c_row = c + static_cast<long long>(out_row) * p.ldc;
+          const bool row_stored = out_row < row_limit;
+          OutT* c_row = c + static_cast<long long>(out_row) * p.ldc;
 #pragma unroll
-            for (int i = 0; i < kPairs; ++i) {
-              const int col = first_col + (i >> 2) * 32 + (i & 3) * 8;
-              if (col < p.n) store_pair<OutT>(c_row + col, acc[r][i], col + 1 < p.n, aligned);
+          for (int block = 0; block < kBlocks; ++block) {
+            const int col = n0 + col_base + block * 32 + 8 * quad;
+            if constexpr (sizeof(OutT) == 2) {
+              uint32_t w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) w[i] = pack_pair<OutT>(acc[r][block * 4 + i]);
+              quad_transpose(w, quad);
+              if (row_stored) {
+                if (aligned && col + 8 <= p.n) {
+                  *reinterpret_cast<uint4*>(c_row + col) = make_uint4(w[0], w[1], w[2], w[3]);
+                } else {
+                  unsigned short* out = reinterpret_cast<unsigned short*>(c_row);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    if (col + 2 * j < p.n) out[col + 2 * j] = static_cast<unsigned short>(w[j] & 0xffffu);
+                    if (col + 2 * j + 1 < p.n) out[col + 2 * j + 1] = static_cast<unsigned short>(w[j] >> 16);
+                  }
+                }
+              }
+            } else {
+              uint32_t wx[4], wy[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                wx[i] = __float_as_uint(acc[r][block * 4 + i].x);
+                wy[i] = __float_as_uint(acc[r][block * 4 + i].y);
+              }
+              quad_transpose(wx, quad);
+              quad_transpose(wy, quad);
+              if (row_stored) {
+                if (aligned && col + 8 <= p.n) {
+                  uint4* out = reinterpret_cast<uint4*>(c_row + col);
+                  out[0] = make_uint4(wx[0], wy[0], wx[1], wy[1]);
+                  out[1] = make_uint4(wx[2], wy[2], wx[3], wy[3]);
+                } else {
+                  uint32_t* out = reinterpret_cast<uint32_t*>(c_row);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    if (col + 2 * j < p.n) out[col + 2 * j] = wx[j];
+                    if (col + 2 * j + 1 < p.n) out[col + 2 * j + 1] = wy[j];
+                  }
+                }
+              }
             }
           }
         }

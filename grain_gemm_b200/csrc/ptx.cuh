@@ -168,6 +168,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
   }
 }
 
+// Warp-collective wait: every lane probes, then waits if needed; the verdict is the same in
+// all lanes.  Issuing warps stay converged this way, so that descriptor and address
+// arithmetic around their tcgen05.mma / TMA instructions runs in the uniform datapath; only
+// the issue itself is left to one elected lane.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, unsigned int site,
+                                               volatile int* abort_flag) {
+  const bool got = mbar_test(bar, parity) || mbar_wait(bar, parity, site, abort_flag);
+  return __all_sync(0xffffffffu, got);
+}
+
 // ---------------------------------------------------------------- TMA
 
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
