@@ -157,6 +157,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
     const int row_group = gather_id >> 3;
     uint32_t stage = 0, phase = 0;
     bool ok = true;
+    const bool tma_leader = warp == 8 && elect_one();
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
       int tile, jg, expert;
       if (!gate_up_item(p, item, channel_groups, tile, jg, expert)) continue;
@@ -187,7 +188,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
             break;
           }
           uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
-          if (warp == 8 && lane == 0) {
+          if (tma_leader) {
             uint8_t* b_dst = a_dst + Shape::kABytes;
             mbar_expect_tx(&full_bar[stage], Shape::kBBytes);
             tma_load_2d(b_dst, &map_w, &full_bar[stage], x, row_gate);
@@ -214,7 +215,10 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
     }
   } else {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The warp walks the loop converged and one elected lane issues, which keeps the
+    // descriptor arithmetic in the uniform datapath.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc = make_idesc_i8(128, BN);
       const uint32_t a_low_base = smem_desc_low(smem_u32(stage_base));
       uint32_t stage = 0, phase = 0;
@@ -223,9 +227,8 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         if (p.tile_expert[item / channel_groups] < 0) continue;
         for (int sub = 0; sub < 2 && ok; ++sub) {
-          for (int slab = 0; slab < slabs && ok; ++slab) {
-            if (!mbar_test(&full_bar[stage], phase) &&
-                !mbar_wait(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
+          for (int slab = 0; slab < slabs; ++slab) {
+            if (!mbar_wait_warp(&full_bar[stage], phase, kSiteMmaFull, abort_flag)) {
               ok = false;
               break;
             }
@@ -235,9 +238,8 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
             tcgen05_fence_after();
             const bool group_start = (slab & 1) == 0;
             if (group_start) {
-              if (!mbar_test(&tmem_empty_bar[buffer], empty_parity) &&
-                  !mbar_wait(&tmem_empty_bar[buffer], empty_parity, kSiteMmaTmemEmpty,
-                             abort_flag)) {
+              if (!mbar_wait_warp(&tmem_empty_bar[buffer], empty_parity, kSiteMmaTmemEmpty,
+                                  abort_flag)) {
                 ok = false;
                 break;
               }
@@ -245,14 +247,16 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
             }
             const uint32_t a_low = a_low_base + stage * (Shape::kStageBytes >> 4);
             const uint32_t b_low = a_low + (Shape::kABytes >> 4);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              umma_i8<1>(tmem_base + buffer * BN, a_low + 2 * j, b_low + 2 * j, idesc,
-                         (group_start && j == 0) ? 0u : 1u);
+            const uint32_t tmem_d = tmem_base + buffer * BN;
+            if (leader) {
+              umma_i8<1>(tmem_d, a_low, b_low, idesc, group_start ? 0u : 1u);
+              umma_i8<1>(tmem_d, a_low + 2, b_low + 2, idesc, 1u);
+              umma_i8<1>(tmem_d, a_low + 4, b_low + 4, idesc, 1u);
+              umma_i8<1>(tmem_d, a_low + 6, b_low + 6, idesc, 1u);
+              umma_commit(&empty_bar[stage]);
+              if (!group_start) umma_commit(&tmem_full_bar[buffer]);
             }
-            umma_commit(&empty_bar[stage]);
             if (!group_start) {
-              umma_commit(&tmem_full_bar[buffer]);
               buffer ^= 1u;
               if (buffer == 0) empty_parity ^= 1u;
             }
