@@ -51,7 +51,8 @@ struct GateUpShape {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStashPitch = 128;   // floats per parked row
   static constexpr int kStashBytesPerCta = 128 * kStashPitch * 4;   // in global memory (L2)
-  static constexpr int kScaleBytes = 2 * 256 * 4;
+  static constexpr int kRingFloats = 256 + 128;   // column scales then row scales of one group
+  static constexpr int kScaleBytes = 2 * kRingFloats * 4;
   static constexpr int kAmaxBytes = 4 * 128 * 4;
   static constexpr int kTokenBytes = 128 * 4;
   static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
@@ -110,7 +111,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
   // The first sub-tile's h waits in global memory (it stays in L2) for the second sub-tile's
   // half of the row maximum; keeping it out of shared memory buys a fourth operand stage.
   float* stash = p.stash + static_cast<size_t>(blockIdx.x) * 128 * Shape::kStashPitch;
-  float* amax_part = sb_ring + 2 * BN;
+  float* amax_part = sb_ring + 2 * Shape::kRingFloats;
   int* tile_tokens = reinterpret_cast<int*>(amax_part + 4 * 128);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(tile_tokens + 128);
   uint64_t* empty_bar = full_bar + kStages;
@@ -272,22 +273,38 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
   } else {
     setmaxnreg_inc<216>();
     // ------------------------------------------------------------ promotion + SwiGLU warps
+    // Fragment layout (tmem_ld_16x256b_x4): warp (quarter, half) drains TMEM lanes
+    // 32*quarter.. of four 32-column blocks; a thread owns tile rows
+    // 32*quarter + lane/4 + 8r (r = 0..3) and, in every block, the column pairs
+    // 8i + 2*(lane%4), +1 (i = 0..3).  Split layout: blocks 0,1 are 64 gate columns of this
+    // half, blocks 2,3 the matching up columns; interleaved: each pair is (gate, up) of one
+    // channel.
     const int half = warp >> 2;
     const int quarter = warp & 3;
     const int tid = threadIdx.x;
-    const int row_in_tile = quarter * 32 + lane;
+    const int fragment_row = lane >> 2;
+    const int quad = lane & 3;
+    const int stage_row = tid & 127;   // tile row whose activation scale this thread stages
     uint32_t group_sequence = 0;
     bool ok = true;
-    float* stash_row = stash + row_in_tile * Shape::kStashPitch + half * 64;
+    float4* stash4 = reinterpret_cast<float4*>(stash) + tid;   // element j at stash4[j * 256]
+    int block_column[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      block_column[b] = p.interleaved ? half * 128 + 32 * b
+                                      : (b < 2 ? half * 64 + 32 * b : 128 + half * 64 + 32 * (b - 2));
+    }
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       int tile, jg, expert;
       if (!gate_up_item(p, item, channel_groups, tile, jg, expert)) continue;
-      const int row = p.tile_row[tile] + row_in_tile;
-      const bool row_ok = row < p.expert_offsets[expert + 1];
-      const long long token = row_ok ? p.order[row] / p.top_k : 0;
-      const float* sa_row = p.scale_x + token * groups;
+      const int row0 = p.tile_row[tile];
+      const int row_end = p.expert_offsets[expert + 1];
+      const bool stage_row_ok = tid < 128 && row0 + stage_row < row_end;
+      const long long stage_token = stage_row_ok ? p.order[row0 + stage_row] / p.top_k : 0;
+      const float* sa_row = p.scale_x + stage_token * groups;
       const float* sb_base = p.scale_w + static_cast<long long>(expert) * groups * 2 * p.intermediate;
-      float amax_first = 0.0f;
+      const int first_row = row0 + quarter * 32 + fragment_row;   // + 8r
+      float amax_first[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
       for (int sub = 0; sub < 2; ++sub) {
         const int channel0 = jg * 256 + sub * 128;
@@ -295,139 +312,199 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
         const int sb_col = p.interleaved ? 2 * channel0 + tid
                                          : (tid < 128 ? channel0 + tid
                                                       : p.intermediate + channel0 + tid - 128);
-        float2 acc2[64];
+        float2 acc[4][16];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc2[i] = make_float2(0.0f, 0.0f);
+        for (int r = 0; r < 4; ++r) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[r][i] = make_float2(0.0f, 0.0f);
+        }
+        // Scale ring slot: [0, 256) column scales by accumulator column, [256, 384) row scales.
         sb_ring[tid] = sb_base[sb_col];
-        float sa_next = row_ok ? sa_row[0] : 0.0f;
+        if (tid < 128) sb_ring[BN + tid] = stage_row_ok ? sa_row[0] : 0.0f;
         named_barrier_sync(1, 256);
 
         for (int g = 0; g < groups; ++g, ++group_sequence) {
-          const float sa = sa_next;
-          float sb_next = 0.0f;
+          const float* slot = sb_ring + (g & 1) * Shape::kRingFloats;
+          float sb_next = 0.0f, sa_next = 0.0f;
           if (g + 1 < groups) {
             sb_next = sb_base[static_cast<long long>(g + 1) * 2 * p.intermediate + sb_col];
-            if (row_ok) sa_next = sa_row[g + 1];
+            if (stage_row_ok) sa_next = sa_row[g + 1];
           }
+          float sa[4];
+#pragma unroll
+          for (int r = 0; r < 4; ++r) sa[r] = slot[BN + quarter * 32 + fragment_row + 8 * r];
           const uint32_t buffer = group_sequence & 1u;
           if (ok && !mbar_wait(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
                                kSiteEpilogueTmemFull, abort_flag)) {
             ok = false;
           }
           tcgen05_fence_after();
-          const float* sb_slot = sb_ring + (g & 1) * BN;
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN;
-          // Split layout: chunks 0,1 are this thread's gate columns, 2,3 its up columns.
-          const int column0 = p.interleaved ? half * 128 : half * 64;
-          const int column1 = column0 + 32;
-          const int column2 = p.interleaved ? half * 128 + 64 : 128 + half * 64;
-          const int column3 = column2 + 32;
-          uint32_t partial_a[32], partial_b[32];
-          if (ok) {
-            tmem_ld_32x32b_x32(taddr + column0, partial_a);
+          const uint32_t taddr_low =
+              tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN;
+          const uint32_t taddr_high = taddr_low + (16u << 16);
+          uint32_t partial_a[16], partial_b[16];
+          float2 sb[4];
+          if (ok) tmem_ld_16x256b_x4(taddr_low + block_column[0], partial_a);
+#pragma unroll
+          for (int fragment = 0; fragment < 8; ++fragment) {
+            if (!ok) break;
+            const int block = fragment >> 1;
+            if ((fragment & 1) == 0) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                sb[i] = *reinterpret_cast<const float2*>(slot + block_column[block] + 8 * i + 2 * quad);
+              }
+            }
             tmem_ld_wait();
-            tmem_ld_32x32b_x32(taddr + column1, partial_b);
-            promote<32>(partial_a, sa, sb_slot + column0, acc2);
-            tmem_ld_wait();
-            tmem_ld_32x32b_x32(taddr + column2, partial_a);
-            promote<32>(partial_b, sa, sb_slot + column1, acc2 + 16);
-            tmem_ld_wait();
-            tmem_ld_32x32b_x32(taddr + column3, partial_b);
-            promote<32>(partial_a, sa, sb_slot + column2, acc2 + 32);
-            tmem_ld_wait();
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
-            promote<32>(partial_b, sa, sb_slot + column3, acc2 + 48);
+            if (fragment + 1 < 8) {
+              const uint32_t next = ((fragment + 1) & 1 ? taddr_high : taddr_low) +
+                                    block_column[(fragment + 1) >> 1];
+              if (fragment & 1) tmem_ld_16x256b_x4(next, partial_a);
+              else tmem_ld_16x256b_x4(next, partial_b);
+            } else {
+              // All of this warp's TMEM reads for the buffer are done: hand it back.
+              tcgen05_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
+            }
+            if (fragment & 1) {
+              promote_fragment(partial_b, sa[2], sa[3], sb, &acc[2][block * 4], &acc[3][block * 4]);
+            } else {
+              promote_fragment(partial_a, sa[0], sa[1], sb, &acc[0][block * 4], &acc[1][block * 4]);
+            }
           }
-          sb_ring[((g + 1) & 1) * BN + tid] = sb_next;
+          float* next_slot = sb_ring + ((g + 1) & 1) * Shape::kRingFloats;
+          next_slot[tid] = sb_next;
+          if (tid < 128) next_slot[BN + tid] = sa_next;
           named_barrier_sync(1, 256);
         }
 
-        // SwiGLU on the rounded gate/up values.  Accumulator i is column i of this thread's
-        // 128: split layout = gate c at i = c and up c at i = 64 + c; interleaved = 2c, 2c + 1.
-        float acc[64];
-        float amax = 0.0f;
+        // SwiGLU on the rounded gate/up values.  h[r][k] is channel (of this sub-tile's 128)
+        //   split:       half*64 + (k/8)*32 + 8*((k%8)/2) + 2*quad + k%2
+        //   interleaved: half*64 + (k/4)*16 + 4*(k%4) + quad
+        float h[4][16];
+        float amax[4];
 #pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 8) {
-          float gate[8], up[8], denominator[8];
-          bool safe = true;
+        for (int r = 0; r < 4; ++r) {
+          float row_amax = 0.0f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int c = c0 + j;
-            const float gate_split = (c & 1) ? acc2[c / 2].y : acc2[c / 2].x;
-            const float up_split = (c & 1) ? acc2[32 + c / 2].y : acc2[32 + c / 2].x;
-            gate[j] = round_through<RoundT>(p.interleaved ? acc2[c].x : gate_split);
-            up[j] = round_through<RoundT>(p.interleaved ? acc2[c].y : up_split);
-            denominator[j] = __fadd_rn(1.0f, expf(-gate[j]));
-            safe = safe && swiglu_division_is_safe(gate[j], denominator[j]);
-          }
-          if (safe) {
+          for (int k0 = 0; k0 < 16; k0 += 8) {
+            float gate[8], up[8], denominator[8];
+            bool safe = true;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float y = reciprocal_by_fma(denominator[j]);
-              acc[c0 + j] = __fmul_rn(divide_by_fma(gate[j], denominator[j], y), up[j]);
+              const int k = k0 + j;
+              // split: k = b*8 + i*2 + e -> gate acc[r][b*4+i].e, up acc[r][(2+b)*4+i].e
+              const float2 gate_pair = acc[r][(k >> 3) * 4 + ((k & 7) >> 1)];
+              const float2 up_pair = acc[r][(2 + (k >> 3)) * 4 + ((k & 7) >> 1)];
+              const float gate_split = (k & 1) ? gate_pair.y : gate_pair.x;
+              const float up_split = (k & 1) ? up_pair.y : up_pair.x;
+              gate[j] = round_through<RoundT>(p.interleaved ? acc[r][k].x : gate_split);
+              up[j] = round_through<RoundT>(p.interleaved ? acc[r][k].y : up_split);
+              denominator[j] = __fadd_rn(1.0f, expf(-gate[j]));
+              safe = safe && swiglu_division_is_safe(gate[j], denominator[j]);
             }
-          } else {
+            if (safe) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              acc[c0 + j] = __fmul_rn(__fdiv_rn(gate[j], denominator[j]), up[j]);
+              for (int j = 0; j < 8; ++j) {
+                const float y = reciprocal_by_fma(denominator[j]);
+                h[r][k0 + j] = __fmul_rn(divide_by_fma(gate[j], denominator[j], y), up[j]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                h[r][k0 + j] = __fmul_rn(__fdiv_rn(gate[j], denominator[j]), up[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) row_amax = fmaxf(row_amax, fabsf(h[r][k0 + j]));
           }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(acc[c0 + j]));
+          // The four lanes of a quad hold the row's other channels of this half.
+          row_amax = fmaxf(row_amax, __shfl_xor_sync(0xffffffffu, row_amax, 1));
+          row_amax = fmaxf(row_amax, __shfl_xor_sync(0xffffffffu, row_amax, 2));
+          amax[r] = row_amax;
+          if (quad == 0) {
+            amax_part[(sub * 2 + half) * 128 + quarter * 32 + fragment_row + 8 * r] = row_amax;
+          }
         }
-        amax_part[(sub * 2 + half) * 128 + row_in_tile] = amax;
         if (sub == 0) {
 #pragma unroll
-          for (int c = 0; c < 64; c += 4)
-            *reinterpret_cast<float4*>(stash_row + c) =
-                make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
-          amax_first = amax;
+          for (int r = 0; r < 4; ++r) {
+#pragma unroll
+            for (int k = 0; k < 16; k += 4) {
+              stash4[(r * 4 + k / 4) * 256] = make_float4(h[r][k], h[r][k + 1], h[r][k + 2], h[r][k + 3]);
+            }
+            amax_first[r] = amax[r];
+          }
         } else {
           named_barrier_sync(1, 256);
-          float row_max = fmaxf(amax, amax_first);
-          row_max = fmaxf(row_max, amax_part[(0 * 2 + (half ^ 1)) * 128 + row_in_tile]);
-          row_max = fmaxf(row_max, amax_part[(1 * 2 + (half ^ 1)) * 128 + row_in_tile]);
-          const float scale = quantize_scale(row_max);
-          if (row_ok && ok) {
-            int8_t* q_row = p.q + static_cast<long long>(row) * p.intermediate + jg * 256;
+          const bool all_ok = __all_sync(0xffffffffu, ok);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int tile_row = quarter * 32 + fragment_row + 8 * r;
+            float row_max = fmaxf(amax[r], amax_first[r]);
+            row_max = fmaxf(row_max, amax_part[(0 * 2 + (half ^ 1)) * 128 + tile_row]);
+            row_max = fmaxf(row_max, amax_part[(1 * 2 + (half ^ 1)) * 128 + tile_row]);
+            const float scale = quantize_scale(row_max);
             const bool by_fma = quantize_division_is_safe(row_max);
             const float y = __frcp_rn(scale);
+            const int row = first_row + 8 * r;
+            const bool row_stored = all_ok && row < row_end;
+            int8_t* q_row = p.q + static_cast<long long>(row) * p.intermediate + jg * 256;
 #pragma unroll
             for (int piece = 0; piece < 2; ++piece) {
-              // piece 0: parked first sub-tile (channels half*64..), piece 1: registers.
-              uint4* dst = reinterpret_cast<uint4*>(q_row + piece * 128 + half * 64);
+              // piece 0: parked first sub-tile (channels 0..127), piece 1: registers.
+              float v[16];
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                float h16[16];
+              for (int k = 0; k < 16; k += 4) {
+                if (piece == 0) {
+                  const float4 parked = stash4[(r * 4 + k / 4) * 256];
+                  v[k] = parked.x; v[k + 1] = parked.y; v[k + 2] = parked.z; v[k + 3] = parked.w;
+                } else {
+                  v[k] = h[r][k]; v[k + 1] = h[r][k + 1]; v[k + 2] = h[r][k + 2]; v[k + 3] = h[r][k + 3];
+                }
+              }
+              uint32_t code[16];
+              if (by_fma) {
 #pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                  const int c = v * 16 + w * 4;
-                  if (piece == 0) {
-                    const float4 parked = *reinterpret_cast<const float4*>(stash_row + c);
-                    h16[w * 4] = parked.x; h16[w * 4 + 1] = parked.y;
-                    h16[w * 4 + 2] = parked.z; h16[w * 4 + 3] = parked.w;
-                  } else {
+                for (int k = 0; k < 16; ++k)
+                  code[k] = static_cast<uint32_t>(quantize_value_by_fma(v[k], scale, y)) & 0xffu;
+              } else {
 #pragma unroll
-                    for (int b = 0; b < 4; ++b) h16[w * 4 + b] = acc[c + b];
+                for (int k = 0; k < 16; ++k)
+                  code[k] = static_cast<uint32_t>(quantize_value(v[k], scale)) & 0xffu;
+              }
+              int8_t* q_piece = q_row + piece * 128 + half * 64;
+              if (p.interleaved) {
+                // Lane `quad` holds channels 16*blk + 4i + quad; after the exchange it holds the
+                // four consecutive channels 16*blk + 4*quad .. +3.
+#pragma unroll
+                for (int blk = 0; blk < 4; ++blk) {
+                  uint32_t w[4] = {code[blk * 4], code[blk * 4 + 1], code[blk * 4 + 2], code[blk * 4 + 3]};
+                  quad_transpose(w, quad);
+                  if (row_stored) {
+                    *reinterpret_cast<uint32_t*>(q_piece + blk * 16 + 4 * quad) =
+                        w[0] | (w[1] << 8) | (w[2] << 16) | (w[3] << 24);
                   }
                 }
-                uint32_t words[4] = {0u, 0u, 0u, 0u};
-                if (by_fma) {
+              } else {
+                // Lane `quad` holds channel pairs 32*b + 8i + 2*quad, +1; after the exchange it
+                // holds the eight consecutive channels 32*b + 8*quad .. +7.
 #pragma unroll
-                  for (int b = 0; b < 16; ++b)
-                    words[b / 4] |= (static_cast<uint32_t>(quantize_value_by_fma(h16[b], scale, y)) & 0xffu)
-                                    << (8 * (b % 4));
-                } else {
+                for (int b = 0; b < 2; ++b) {
+                  uint32_t w[4];
 #pragma unroll
-                  for (int b = 0; b < 16; ++b)
-                    words[b / 4] |= (static_cast<uint32_t>(quantize_value(h16[b], scale)) & 0xffu)
-                                    << (8 * (b % 4));
+                  for (int i = 0; i < 4; ++i) w[i] = code[b * 8 + 2 * i] | (code[b * 8 + 2 * i + 1] << 8);
+                  quad_transpose(w, quad);
+                  if (row_stored) {
+                    *reinterpret_cast<uint2*>(q_piece + b * 32 + 8 * quad) =
+                        make_uint2(w[0] | (w[1] << 16), w[2] | (w[3] << 16));
+                  }
                 }
-                dst[v] = make_uint4(words[0], words[1], words[2], words[3]);
               }
             }
-            if (half == 0) p.s[static_cast<long long>(row) * channel_groups + jg] = scale;
+            if (row_stored && half == 0 && quad == 0) {
+              p.s[static_cast<long long>(row) * channel_groups + jg] = scale;
+            }
           }
         }
       }
