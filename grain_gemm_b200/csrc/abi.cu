@@ -17,7 +17,7 @@
 
 namespace gg {
 
-constexpr int kAbiVersion = 1;
+constexpr int kAbiVersion = 2;
 
 // ---------------------------------------------------------------- host helpers
 
@@ -529,11 +529,15 @@ int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, 
   return static_cast<int>(cudaGetLastError());
 }
 
-size_t gg_moe_gate_up_scratch_bytes(int assignments, int intermediate, int tile_rows) {
+// Tensor-core path: [activation rows in sorted order | their scales].
+size_t gg_moe_gate_up_scratch_bytes(int assignments, int hidden, int intermediate, int tile_rows) {
+  const size_t slots = static_cast<size_t>(assignments > 0 ? assignments : 0);
   if (tile_rows == 128) {
-    return static_cast<size_t>(gg::sm_count()) * gg::GateUpShape::kStashBytesPerCta;
+    const size_t rows = slots * static_cast<size_t>(hidden > 0 ? hidden : 0);
+    const size_t scales = slots * static_cast<size_t>(hidden > 0 ? hidden / 256 : 0) * 4;
+    return ((rows + 255) & ~static_cast<size_t>(255)) + scales;
   }
-  return static_cast<size_t>(assignments > 0 ? assignments : 0) * 2 * intermediate * 2;
+  return slots * 2 * intermediate * 2;
 }
 
 int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const void* scale_w1,
@@ -554,22 +558,36 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
         !gg::aligned16(gate_up_scratch)) {
       return static_cast<int>(cudaErrorInvalidValue);
     }
-    CUtensorMap map_w;
-    const int status = gg::encode_int8_rows(&map_w, w1, static_cast<long long>(experts) * 2 * intermediate,
-                                            hidden, hidden, 128);
+    // Stage 2a: activation rows and their scales in sorted-slot order.
+    uint8_t* scratch = static_cast<uint8_t*>(gate_up_scratch);
+    int8_t* sorted_x = reinterpret_cast<int8_t*>(scratch);
+    const size_t row_bytes = (static_cast<size_t>(slots) * hidden + 255) & ~static_cast<size_t>(255);
+    float* sorted_scale = reinterpret_cast<float*>(scratch + row_bytes);
+    {
+      const long long blocks = (slots + 7) / 8;
+      const int limit = gg::sm_count() * 8;
+      gg::gather_rows_kernel<<<static_cast<int>(blocks < limit ? blocks : limit), 256, 0, stream>>>(
+          static_cast<const int8_t*>(x), static_cast<const float*>(scale_x),
+          static_cast<const long long*>(order), static_cast<const int*>(offsets), experts, top_k,
+          hidden, sorted_x, sorted_scale);
+      const cudaError_t error = cudaGetLastError();
+      if (error != cudaSuccess) return static_cast<int>(error);
+    }
+    CUtensorMap map_x, map_w;
+    int status = gg::encode_int8_rows(&map_x, sorted_x, slots, hidden, hidden, 128);
+    if (status) return status;
+    status = gg::encode_int8_rows(&map_w, w1, static_cast<long long>(experts) * 2 * intermediate,
+                                  hidden, hidden, 128);
     if (status) return status;
     gg::GateUpParams p = {};
-    p.x = static_cast<const int8_t*>(x);
-    p.scale_x = static_cast<const float*>(scale_x);
+    p.sorted_scale = sorted_scale;
     p.scale_w = static_cast<const float*>(scale_w1);
-    p.order = static_cast<const long long*>(order);
     p.expert_offsets = static_cast<const int*>(offsets);
     p.tile_expert = static_cast<const int*>(tile_expert);
     p.tile_row = static_cast<const int*>(tile_row);
     p.q = static_cast<int8_t*>(q);
     p.s = static_cast<float*>(s);
-    p.stash = static_cast<float*>(gate_up_scratch);
-    p.top_k = top_k; p.hidden = hidden; p.intermediate = intermediate;
+    p.hidden = hidden; p.intermediate = intermediate;
     p.max_tiles = tile_capacity; p.interleaved = interleaved;
     const long long items = static_cast<long long>(tile_capacity) * (intermediate / 256);
     const int grid = static_cast<int>(items < gg::sm_count() ? items : gg::sm_count());
@@ -579,13 +597,13 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
       error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    gg::GateUpShape::kSmemBytes);
       if (error != cudaSuccess) return static_cast<int>(error);
-      kernel<<<grid, 384, gg::GateUpShape::kSmemBytes, stream>>>(map_w, p);
+      kernel<<<grid, 384, gg::GateUpShape::kSmemBytes, stream>>>(map_x, map_w, p);
     } else {
       auto kernel = gg::moe_gate_up_tc_kernel<__half>;
       error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    gg::GateUpShape::kSmemBytes);
       if (error != cudaSuccess) return static_cast<int>(error);
-      kernel<<<grid, 384, gg::GateUpShape::kSmemBytes, stream>>>(map_w, p);
+      kernel<<<grid, 384, gg::GateUpShape::kSmemBytes, stream>>>(map_x, map_w, p);
     }
     return static_cast<int>(cudaGetLastError());
   }

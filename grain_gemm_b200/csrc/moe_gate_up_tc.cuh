@@ -7,18 +7,18 @@
 //   h[c]      = silu(gate[c]) * up[c]                       (FP32, every operation rounded)
 //   scale     = max(max_c |h[c]|, 1e-12) / 127 ;  q[c] = clamp(nearbyint(h[c]/scale), +-127)
 // i.e. src/grain_gemm/kernels/moe.py:359-393 (ragged GEMM with SOURCE_IS_TOKEN) followed by
-// :564-601 (SwiGLU + requantisation) of the reference, without the [S, 2I] intermediate and
-// without an expert-expanded copy of x: the token rows are gathered by the sorted route index
-// straight into the swizzled shared-memory operand tile.
+// :564-601 (SwiGLU + requantisation) of the reference, without the [S, 2I] intermediate.  The
+// token rows are first copied once into sorted-slot order (gather_rows_kernel), so that every
+// operand tile of this kernel arrives by TMA: gathering rows with 16-byte cp.async inside the
+// kernel re-fetched each row tile for every 128-channel block and loaded the load/store
+// pipe, which the promotion warps also need.
 //
 // Work item = (128-row tile of one expert, 256-channel group), processed as two sub-tiles of
 // 128 channels; a sub-tile is one N = 256 accumulator (128 gate + 128 up columns) in TMEM.
-//   warps 8, 10, 11   producers: 16-byte cp.async gather of the x rows (96 threads); lane 0 of
-//             warp 8 also issues the TMA loads of the two weight boxes
+//   warp 8    TMA producer: per stage one box of sorted activation rows, two weight boxes
 //   warp 9    MMA issuer (tcgen05.mma kind::i8, two TMEM buffers)
-//   warps 0-7 promotion per K group, then SwiGLU; the first sub-tile's h is parked in a per-CTA
-//             global scratch (L2 resident) until the second sub-tile supplies the other half of
-//             the row maximum.
+//   warps 0-7 promotion per K group, then SwiGLU; the first sub-tile's h is parked in shared
+//             memory until the second sub-tile supplies the other half of the row maximum.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -31,46 +31,30 @@
 namespace gg {
 
 struct GateUpParams {
-  const int8_t* x;            // [T, H]
-  const float* scale_x;       // [T, H/256]
+  const float* sorted_scale;  // [S, H/256] row scales in sorted-slot order
   const float* scale_w;       // [E, H/256, 2I]
-  const long long* order;     // [S]
   const int* expert_offsets;  // [E+1]
   const int* tile_expert;     // [max_tiles]
   const int* tile_row;        // [max_tiles]
   int8_t* q;                  // [S, I]
   float* s;                   // [S, I/256]
-  float* stash;               // [CTAs, 128, 128] parking space for the first sub-tile's h
-  int top_k, hidden, intermediate, max_tiles, interleaved;
+  int hidden, intermediate, max_tiles, interleaved;
 };
 
 struct GateUpShape {
-  static constexpr int kStages = 4;
+  static constexpr int kStages = 3;
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBBytes = 256 * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStashPitch = 128;   // floats per parked row
-  static constexpr int kStashBytesPerCta = 128 * kStashPitch * 4;   // in global memory (L2)
+  static constexpr int kStashBytes = 256 * 64 * 4;   // 64 parked FP32 values per promotion thread
   static constexpr int kRingFloats = 256 + 128;   // column scales then row scales of one group
   static constexpr int kScaleBytes = 2 * kRingFloats * 4;
   static constexpr int kAmaxBytes = 4 * 128 * 4;
   static constexpr int kTokenBytes = 128 * 4;
   static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kAmaxBytes +
-                                    kTokenBytes + kBarrierBytes;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStashBytes + kScaleBytes +
+                                    kAmaxBytes + kTokenBytes + kBarrierBytes;
 };
-
-__device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_dst, const void* src, bool valid) {
-  const uint32_t bytes = valid ? 16u : 0u;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(src), "r"(bytes)
-               : "memory");
-}
-// Makes `bar` receive one (pre-counted) arrival once all cp.async issued so far by this
-// thread have completed.
-__device__ __forceinline__ void cp_async_arrive_on(uint64_t* bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
 
 // Work item -> (row tile, channel group).  Items of one expert are consecutive and ordered
 // channel-group-major: neighbouring CTAs work on different row tiles of the same expert
@@ -98,7 +82,8 @@ __device__ __forceinline__ float round_through(float v) {
 
 template <typename RoundT>
 __global__ void __launch_bounds__(384, 1)
-moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpParams p) {
+moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
+                      const __grid_constant__ CUtensorMap map_w, const GateUpParams p) {
   using Shape = GateUpShape;
   constexpr int kStages = Shape::kStages;
   constexpr int BN = 256;
@@ -107,10 +92,9 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* stage_base = smem;
-  float* sb_ring = reinterpret_cast<float*>(smem + kStages * Shape::kStageBytes);
-  // The first sub-tile's h waits in global memory (it stays in L2) for the second sub-tile's
-  // half of the row maximum; keeping it out of shared memory buys a fourth operand stage.
-  float* stash = p.stash + static_cast<size_t>(blockIdx.x) * 128 * Shape::kStashPitch;
+  // The first sub-tile's h waits here for the second sub-tile's half of the row maximum.
+  float* stash = reinterpret_cast<float*>(smem + kStages * Shape::kStageBytes);
+  float* sb_ring = stash + Shape::kStashBytes / 4;
   float* amax_part = sb_ring + 2 * Shape::kRingFloats;
   int* tile_tokens = reinterpret_cast<int*>(amax_part + 4 * 128);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(tile_tokens + 128);
@@ -129,7 +113,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(&full_bar[i], 97);  // 96 gather threads + the TMA transaction arrival
+      mbar_init(&full_bar[i], 1);   // the producer's arrive.expect_tx; the TMA bytes complete it
       mbar_init(&empty_bar[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -139,7 +123,10 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 8 && lane == 0) prefetch_tensormap(&map_w);
+  if (warp == 8 && lane == 0) {
+    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&map_w);
+  }
   if (warp == 9) tmem_alloc<1>(tmem_holder, 512);
   tcgen05_fence_before();
   __syncthreads();
@@ -150,66 +137,39 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
   if (warp >= 8) {
   setmaxnreg_dec<64>();
   if (warp != 9) {
-    // ------------------------------------------------------------ producers (warps 8, 10, 11)
-    // 96 gather threads: thread g copies 16-byte chunk (g & 7) of rows (g >> 3) + 12 * i.
-    // Lane 0 of warp 8 also issues the TMA loads of the two weight boxes.
-    const int gather_id = (warp == 8 ? 0 : warp - 9) * 32 + lane;
-    const int chunk = gather_id & 7;
-    const int row_group = gather_id >> 3;
-    uint32_t stage = 0, phase = 0;
-    bool ok = true;
-    const bool tma_leader = warp == 8 && elect_one();
-    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-      int tile, jg, expert;
-      if (!gate_up_item(p, item, channel_groups, tile, jg, expert)) continue;
-      const int row0 = p.tile_row[tile];
-      const int row_end = p.expert_offsets[expert + 1];
-      const int8_t* source[11];
-      uint32_t valid_mask = 0;
-#pragma unroll
-      for (int i = 0; i < 11; ++i) {
-        const int r = row_group + 12 * i;
-        const int row = row0 + r;
-        const bool valid = r < 128 && row < row_end;
-        const long long token = valid ? p.order[row] / p.top_k : 0;
-        source[i] = p.x + token * p.hidden + chunk * 16;
-        valid_mask |= valid ? (1u << i) : 0u;
-      }
-      for (int sub = 0; sub < 2 && ok; ++sub) {
-        const int channel0 = jg * 256 + sub * 128;
-        const int w_base = expert * 2 * p.intermediate;
-        const int row_gate = p.interleaved ? w_base + 2 * channel0 : w_base + channel0;
-        const int row_up = p.interleaved ? row_gate + 128 : w_base + p.intermediate + channel0;
-        for (int slab = 0, x = 0; slab < slabs; ++slab, x += 128) {
-          // Every lane waits; the vote keeps the warp's control flow uniform on failure.
-          const bool got = mbar_test(&empty_bar[stage], phase ^ 1u) ||
-                           mbar_wait(&empty_bar[stage], phase ^ 1u, kSiteProducerEmpty, abort_flag);
-          if (!__all_sync(0xffffffffu, got)) {
-            ok = false;
-            break;
-          }
-          uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
-          if (tma_leader) {
-            uint8_t* b_dst = a_dst + Shape::kABytes;
-            mbar_expect_tx(&full_bar[stage], Shape::kBBytes);
-            tma_load_2d(b_dst, &map_w, &full_bar[stage], x, row_gate);
-            tma_load_2d(b_dst + 128 * 128, &map_w, &full_bar[stage], x, row_up);
-          }
-          const uint32_t a_smem = smem_u32(a_dst);
-#pragma unroll
-          for (int i = 0; i < 11; ++i) {
-            const int r = row_group + 12 * i;
-            if (r < 128) {
-              cp_async_16_zfill(a_smem + r * 128 + ((chunk ^ (r & 7)) << 4), source[i] + x,
-                                (valid_mask >> i) & 1u);
+    // ------------------------------------------------------------ TMA producer (warp 8)
+    // Three boxes per stage: 128 sorted activation rows, 128 gate and 128 up weight rows.
+    // The warp walks the ring converged; one elected lane issues.  Warps 10 and 11 idle.
+    if (warp == 8) {
+      const bool leader = elect_one();
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        int tile, jg, expert;
+        if (!gate_up_item(p, item, channel_groups, tile, jg, expert)) continue;
+        const int row0 = p.tile_row[tile];
+        for (int sub = 0; sub < 2 && ok; ++sub) {
+          const int channel0 = jg * 256 + sub * 128;
+          const int w_base = expert * 2 * p.intermediate;
+          const int row_gate = p.interleaved ? w_base + 2 * channel0 : w_base + channel0;
+          const int row_up = p.interleaved ? row_gate + 128 : w_base + p.intermediate + channel0;
+          for (int slab = 0, x = 0; slab < slabs; ++slab, x += 128) {
+            if (!mbar_wait_warp(&empty_bar[stage], phase ^ 1u, kSiteProducerEmpty, abort_flag)) {
+              ok = false;
+              break;
             }
-          }
-          // The barrier receives this thread's arrival when its copies above have landed;
-          // the thread itself goes straight on to the next slab.
-          cp_async_arrive_on(&full_bar[stage]);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
+            if (leader) {
+              uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
+              uint8_t* b_dst = a_dst + Shape::kABytes;
+              mbar_expect_tx(&full_bar[stage], Shape::kStageBytes);
+              tma_load_2d(a_dst, &map_x, &full_bar[stage], x, row0);
+              tma_load_2d(b_dst, &map_w, &full_bar[stage], x, row_gate);
+              tma_load_2d(b_dst + 128 * 128, &map_w, &full_bar[stage], x, row_up);
+            }
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
       }
@@ -233,9 +193,6 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
               ok = false;
               break;
             }
-            // The x rows were written by cp.async (generic proxy); order them before the
-            // tensor core's reads (async proxy).
-            fence_proxy_async();
             tcgen05_fence_after();
             const bool group_start = (slab & 1) == 0;
             if (group_start) {
@@ -300,8 +257,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_w, const GateUpPar
       const int row0 = p.tile_row[tile];
       const int row_end = p.expert_offsets[expert + 1];
       const bool stage_row_ok = tid < 128 && row0 + stage_row < row_end;
-      const long long stage_token = stage_row_ok ? p.order[row0 + stage_row] / p.top_k : 0;
-      const float* sa_row = p.scale_x + stage_token * groups;
+      const float* sa_row = p.sorted_scale + static_cast<long long>(row0 + stage_row) * groups;
       const float* sb_base = p.scale_w + static_cast<long long>(expert) * groups * 2 * p.intermediate;
       const int first_row = row0 + quarter * 32 + fragment_row;   // + 8r
       float amax_first[4] = {0.0f, 0.0f, 0.0f, 0.0f};

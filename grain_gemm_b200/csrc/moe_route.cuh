@@ -206,6 +206,31 @@ moe_tiles_kernel(const int* __restrict__ offsets, int experts, int tile_rows, in
 
 // ------------------------------------------------------------------ SwiGLU + requantisation
 
+// Activation rows and their scales in sorted-slot order, for the valid slots only:
+// sorted_x[slot, :] = x[order[slot] / top_k, :] and likewise for the row scales, so that the
+// fused Gate/Up kernel can fetch whole 128-row operand tiles by TMA.  One warp per slot; a
+// row is `hidden` bytes (a multiple of 256) moved as 16-byte vectors.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const int8_t* __restrict__ x, const float* __restrict__ scale_x,
+                   const long long* __restrict__ order, const int* __restrict__ offsets,
+                   int experts, int top_k, int hidden, int8_t* __restrict__ sorted_x,
+                   float* __restrict__ sorted_scale) {
+  const int valid = offsets[experts];
+  const int lane = threadIdx.x & 31;
+  const int groups = hidden / 256;
+  const int vectors = hidden / 16;
+  for (long long slot = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); slot < valid;
+       slot += static_cast<long long>(gridDim.x) * 8) {
+    const long long token = order[slot] / top_k;
+    const uint4* source = reinterpret_cast<const uint4*>(x + token * hidden);
+    uint4* destination = reinterpret_cast<uint4*>(sorted_x + slot * hidden);
+    for (int i = lane; i < vectors; i += 32) destination[i] = source[i];
+    for (int g = lane; g < groups; g += 32) {
+      sorted_scale[slot * groups + g] = scale_x[token * groups + g];
+    }
+  }
+}
+
 // h = silu(gate) * up with every operation rounded separately (no FMA contraction), as in
 // src/grain_gemm/kernels/moe.py:594 of the reference (div_rn(g, 1 + exp(-g)) * u).
 __device__ __forceinline__ float swiglu_value(float gate, float up) {

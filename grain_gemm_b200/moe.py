@@ -210,7 +210,7 @@ def gate_up_swiglu_quantize(hidden_states, scale_x, w1_linear, scale_gate_up, ro
     qh = torch.empty((slots, intermediate), dtype=torch.int8, device=device)
     sh = torch.empty((slots, intermediate // 256), dtype=torch.float32, device=device)
     with torch.cuda.device(device):
-        scratch_bytes = lib.gg_moe_gate_up_scratch_bytes(slots, intermediate, routes.tile_rows)
+        scratch_bytes = lib.gg_moe_gate_up_scratch_bytes(slots, hidden, intermediate, routes.tile_rows)
     scratch = torch.empty((max(scratch_bytes, 16),), dtype=torch.uint8, device=device)
     _loader.check(lib.gg_moe_gate_up(
         _loader.pointer(hidden_states), _loader.pointer(scale_x), _loader.pointer(w1_linear),

@@ -159,14 +159,15 @@ int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, 
  * w1: Linear [E,2I,H] contiguous int8; scale_w1: [E,H/256,2I] fp32.  interleaved != 0 means
  * the 2I dimension is ordered [g0,u0,g1,u1,...].  tile_rows must be the value given to
  * gg_moe_tiles: 128 selects the fused tensor-core kernel (needs 16-byte aligned x and w1),
- * 32 the CUDA-core path.  gate_up_scratch must hold gg_moe_gate_up_scratch_bytes() bytes: a
- * per-SM parking area for the fused kernel, the [S,2I] gate/up matrix of out_dtype for the
- * CUDA-core path.
+ * 32 the CUDA-core path.  gate_up_scratch must hold gg_moe_gate_up_scratch_bytes() bytes
+ * (16-byte aligned): for the fused kernel the activation rows [S,H] and their scales in
+ * sorted-slot order, which a small copy kernel fills first so that all operand tiles arrive
+ * by TMA; for the CUDA-core path the [S,2I] gate/up matrix of out_dtype.
  * Replaces ragged_gemm + swiglu_quantize (src/grain_gemm/moe.py:298-304) and
  * grain_moe_gather_launch / grain_moe_interleaved_launch
  * (csrc/sm110/int8_g256_moe_gather.cu:380, int8_g256_moe_interleaved.cu:372).
  */
-size_t gg_moe_gate_up_scratch_bytes(int assignments, int intermediate, int tile_rows);
+size_t gg_moe_gate_up_scratch_bytes(int assignments, int hidden, int intermediate, int tile_rows);
 int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const void* scale_w1,
                    const void* order, const void* offsets, const void* tile_expert,
                    const void* tile_row, int tile_capacity, int tile_rows, void* q, void* s,
