@@ -251,7 +251,7 @@ def run_moe(args, rank, world, device, barrier):
                 "h2d_bytes_per_step": world * sum(t.numel() * t.element_size() for t in host.values()),
                 "d2h_bytes_per_step": world * host_out.numel() * host_out.element_size(),
                 "ms_per_step": e2e_ms},
-        "gpu_launches_per_step": 7 if world == 1 else 12,
+        "gpu_launches_per_step": 8 if world == 1 else 13,
     }
     if stages is not None:
         report["stage_ms"] = stages
