@@ -48,12 +48,12 @@ struct GateUpShape {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStashBytes = 256 * 64 * 4;   // 64 parked FP32 values per promotion thread
   static constexpr int kRingFloats = 256 + 128;   // column scales then row scales of one group
-  static constexpr int kScaleBytes = 2 * kRingFloats * 4;
+  static constexpr int kScaleSlots = 4;
+  static constexpr int kScaleBytes = kScaleSlots * kRingFloats * 4;
   static constexpr int kAmaxBytes = 4 * 128 * 4;
-  static constexpr int kTokenBytes = 128 * 4;
-  static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kBarrierBytes = (2 * kStages + 4 + 2 * kScaleSlots) * 8 + 16;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStashBytes + kScaleBytes +
-                                    kAmaxBytes + kTokenBytes + kBarrierBytes;
+                                    kAmaxBytes + kBarrierBytes;
 };
 
 // Work item -> (row tile, channel group).  Items of one expert are consecutive and ordered
@@ -95,13 +95,14 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   // The first sub-tile's h waits here for the second sub-tile's half of the row maximum.
   float* stash = reinterpret_cast<float*>(smem + kStages * Shape::kStageBytes);
   float* sb_ring = stash + Shape::kStashBytes / 4;
-  float* amax_part = sb_ring + 2 * Shape::kRingFloats;
-  int* tile_tokens = reinterpret_cast<int*>(amax_part + 4 * 128);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tile_tokens + 128);
+  float* amax_part = sb_ring + Shape::kScaleSlots * Shape::kRingFloats;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(amax_part + 4 * 128);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full_bar = empty_bar + kStages;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  uint64_t* scale_full_bar = tmem_empty_bar + 2;
+  uint64_t* scale_empty_bar = scale_full_bar + Shape::kScaleSlots;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(scale_empty_bar + Shape::kScaleSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -119,6 +120,10 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tmem_full_bar[i], 1);
       mbar_init(&tmem_empty_bar[i], 8);
+    }
+    for (int i = 0; i < Shape::kScaleSlots; ++i) {
+      mbar_init(&scale_full_bar[i], 32);   // every lane of the scale warp
+      mbar_init(&scale_empty_bar[i], 8);   // one arrival per promotion warp
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -139,7 +144,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   if (warp != 9) {
     // ------------------------------------------------------------ TMA producer (warp 8)
     // Three boxes per stage: 128 sorted activation rows, 128 gate and 128 up weight rows.
-    // The warp walks the ring converged; one elected lane issues.  Warps 10 and 11 idle.
+    // The warp walks the ring converged; one elected lane issues.  Warp 11 idles.
     if (warp == 8) {
       const bool leader = elect_one();
       uint32_t stage = 0, phase = 0;
@@ -170,6 +175,58 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
               stage = 0;
               phase ^= 1u;
             }
+          }
+        }
+      }
+    } else if (warp == 10) {
+      // ---------------------------------------------------------- scale staging warp
+      // Copies each group's 256 column scales (by accumulator column) and 128 row scales into a
+      // shared-memory ring, one group ahead in registers, so that the promotion warps neither
+      // wait on global memory nor on each other.
+      uint32_t slot = 0, phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        int tile, jg, expert;
+        if (!gate_up_item(p, item, channel_groups, tile, jg, expert)) continue;
+        const int row0 = p.tile_row[tile];
+        const int row_end = p.expert_offsets[expert + 1];
+        const float* sb_base = p.scale_w + static_cast<long long>(expert) * groups * 2 * p.intermediate;
+        for (int sub = 0; sub < 2 && ok; ++sub) {
+          const int channel0 = jg * 256 + sub * 128;
+          float sb_next[8], sa_next[4];
+          auto fetch = [&](int g) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int c = lane + 32 * i;   // accumulator column
+              const int sb_col = p.interleaved ? 2 * channel0 + c
+                                               : (i < 4 ? channel0 + c : p.intermediate + channel0 + c - 128);
+              sb_next[i] = sb_base[static_cast<long long>(g) * 2 * p.intermediate + sb_col];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int r = row0 + lane + 32 * i;
+              sa_next[i] = r < row_end ? p.sorted_scale[static_cast<long long>(r) * groups + g] : 0.0f;
+            }
+          };
+          fetch(0);
+          for (int g = 0; g < groups; ++g) {
+            const bool got = mbar_test(&scale_empty_bar[slot], phase ^ 1u) ||
+                             mbar_wait(&scale_empty_bar[slot], phase ^ 1u, kSiteScaleEmpty, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) {
+              ok = false;
+              break;
+            }
+            float* destination = sb_ring + slot * Shape::kRingFloats;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) destination[lane + 32 * i] = sb_next[i];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) destination[BN + lane + 32 * i] = sa_next[i];
+            mbar_arrive(&scale_full_bar[slot]);
+            if (++slot == Shape::kScaleSlots) {
+              slot = 0;
+              phase ^= 1u;
+            }
+            if (g + 1 < groups) fetch(g + 1);
           }
         }
       }
@@ -241,8 +298,8 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     const int tid = threadIdx.x;
     const int fragment_row = lane >> 2;
     const int quad = lane & 3;
-    const int stage_row = tid & 127;   // tile row whose activation scale this thread stages
     uint32_t group_sequence = 0;
+    uint32_t scale_slot = 0, scale_phase = 0;
     bool ok = true;
     float4* stash4 = reinterpret_cast<float4*>(stash) + tid;   // element j at stash4[j * 256]
     int block_column[4];
@@ -256,36 +313,24 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       if (!gate_up_item(p, item, channel_groups, tile, jg, expert)) continue;
       const int row0 = p.tile_row[tile];
       const int row_end = p.expert_offsets[expert + 1];
-      const bool stage_row_ok = tid < 128 && row0 + stage_row < row_end;
-      const float* sa_row = p.sorted_scale + static_cast<long long>(row0 + stage_row) * groups;
-      const float* sb_base = p.scale_w + static_cast<long long>(expert) * groups * 2 * p.intermediate;
       const int first_row = row0 + quarter * 32 + fragment_row;   // + 8r
       float amax_first[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
       for (int sub = 0; sub < 2; ++sub) {
-        const int channel0 = jg * 256 + sub * 128;
-        // Accumulator column `tid` of this sub-tile corresponds to this weight column.
-        const int sb_col = p.interleaved ? 2 * channel0 + tid
-                                         : (tid < 128 ? channel0 + tid
-                                                      : p.intermediate + channel0 + tid - 128);
         float2 acc[4][16];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) acc[r][i] = make_float2(0.0f, 0.0f);
         }
-        // Scale ring slot: [0, 256) column scales by accumulator column, [256, 384) row scales.
-        sb_ring[tid] = sb_base[sb_col];
-        if (tid < 128) sb_ring[BN + tid] = stage_row_ok ? sa_row[0] : 0.0f;
-        named_barrier_sync(1, 256);
-
         for (int g = 0; g < groups; ++g, ++group_sequence) {
-          const float* slot = sb_ring + (g & 1) * Shape::kRingFloats;
-          float sb_next = 0.0f, sa_next = 0.0f;
-          if (g + 1 < groups) {
-            sb_next = sb_base[static_cast<long long>(g + 1) * 2 * p.intermediate + sb_col];
-            if (stage_row_ok) sa_next = sa_row[g + 1];
+          // This group's scales, staged by the scale warp: [0, 256) column scales by
+          // accumulator column, [256, 384) row scales by tile row.
+          if (ok && !mbar_test(&scale_full_bar[scale_slot], scale_phase) &&
+              !mbar_wait(&scale_full_bar[scale_slot], scale_phase, kSiteScaleFull, abort_flag)) {
+            ok = false;
           }
+          const float* slot = sb_ring + scale_slot * Shape::kRingFloats;
           float sa[4];
 #pragma unroll
           for (int r = 0; r < 4; ++r) sa[r] = slot[BN + quarter * 32 + fragment_row + 8 * r];
@@ -329,10 +374,13 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
               promote_fragment(partial_a, sa[0], sa[1], sb, &acc[0][block * 4], &acc[1][block * 4]);
             }
           }
-          float* next_slot = sb_ring + ((g + 1) & 1) * Shape::kRingFloats;
-          next_slot[tid] = sb_next;
-          if (tid < 128) next_slot[BN + tid] = sa_next;
-          named_barrier_sync(1, 256);
+          // Every lane has consumed the slot's values (they fed the arithmetic above).
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&scale_empty_bar[scale_slot]);
+          if (++scale_slot == Shape::kScaleSlots) {
+            scale_slot = 0;
+            scale_phase ^= 1u;
+          }
         }
 
         // SwiGLU on the rounded gate/up values.  h[r][k] is channel (of this sub-tile's 128)
