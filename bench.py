@@ -35,7 +35,7 @@ sys.path.insert(0, str(ROOT))
 
 # DRAM traffic of one launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum
 # from the ncu capture summarised in profiles/); None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"gemm_g256_m8192_n8192_k8192_bf16": 354455296}
+NCU_TRAFFIC_BYTES = {"gemm_g256_m8192_n8192_k8192_bf16": 365767168}
 
 
 def parse():
@@ -79,6 +79,7 @@ class ClockSampler:
         self.device_index = device_index
         self.process = None
         self.lines = []
+        self.skip = 0
 
     def __enter__(self):
         try:
@@ -88,6 +89,12 @@ class ClockSampler:
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            # nvidia-smi needs a moment to start (longer on an 8-GPU box): wait for its first
+            # line so that a short timed region is still sampled.
+            deadline = time.time() + 5.0
+            while not self.lines and time.time() < deadline:
+                time.sleep(0.01)
+            self.skip = len(self.lines)
         except OSError:
             self.process = None
         return self
@@ -105,7 +112,10 @@ class ClockSampler:
     def summary(self):
         clocks, maxima, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        # Lines read before the timed region began describe an idle GPU; use them only when the
+        # region was too short to be sampled at all.
+        lines = self.lines[self.skip:] or self.lines
+        for line in lines:
             fields = [f.strip() for f in line.split(",")]
             if len(fields) < 9:
                 continue
