@@ -529,13 +529,14 @@ int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, 
   return static_cast<int>(cudaGetLastError());
 }
 
-// Tensor-core path: [activation rows in sorted order | their scales].
+// Tensor-core path: [activation rows in sorted order | their scales | SiLU table].
 size_t gg_moe_gate_up_scratch_bytes(int assignments, int hidden, int intermediate, int tile_rows) {
   const size_t slots = static_cast<size_t>(assignments > 0 ? assignments : 0);
   if (tile_rows == 128) {
     const size_t rows = slots * static_cast<size_t>(hidden > 0 ? hidden : 0);
     const size_t scales = slots * static_cast<size_t>(hidden > 0 ? hidden / 256 : 0) * 4;
-    return ((rows + 255) & ~static_cast<size_t>(255)) + scales;
+    return ((rows + 255) & ~static_cast<size_t>(255)) + ((scales + 255) & ~static_cast<size_t>(255)) +
+           65536 * sizeof(float);
   }
   return slots * 2 * intermediate * 2;
 }
@@ -563,13 +564,16 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
     int8_t* sorted_x = reinterpret_cast<int8_t*>(scratch);
     const size_t row_bytes = (static_cast<size_t>(slots) * hidden + 255) & ~static_cast<size_t>(255);
     float* sorted_scale = reinterpret_cast<float*>(scratch + row_bytes);
+    const size_t scale_bytes =
+        (static_cast<size_t>(slots) * (hidden / 256) * 4 + 255) & ~static_cast<size_t>(255);
+    float* silu_table = reinterpret_cast<float*>(scratch + row_bytes + scale_bytes);
     {
       const long long blocks = (slots + 7) / 8;
       const int limit = gg::sm_count() * 8;
       gg::gather_rows_kernel<<<static_cast<int>(blocks < limit ? blocks : limit), 256, 0, stream>>>(
           static_cast<const int8_t*>(x), static_cast<const float*>(scale_x),
           static_cast<const long long*>(order), static_cast<const int*>(offsets), experts, top_k,
-          hidden, sorted_x, sorted_scale);
+          hidden, sorted_x, sorted_scale, silu_table, out_dtype == GG_OUT_FP16 ? 1 : 0);
       const cudaError_t error = cudaGetLastError();
       if (error != cudaSuccess) return static_cast<int>(error);
     }
@@ -581,6 +585,7 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
     if (status) return status;
     gg::GateUpParams p = {};
     p.sorted_scale = sorted_scale;
+    p.silu_table = silu_table;
     p.scale_w = static_cast<const float*>(scale_w1);
     p.expert_offsets = static_cast<const int*>(offsets);
     p.tile_expert = static_cast<const int*>(tile_expert);
@@ -705,6 +710,37 @@ int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_
   p.b_expert_stride = static_cast<long long>(hidden) * intermediate;
   p.sb_expert_stride = static_cast<long long>(intermediate / 256) * hidden;
   return gg::launch_simt_dtype<true>(p, tile_capacity, out_dtype, stream);
+}
+
+int gg_quantize_rows(const void* x, int in_dtype, long long rows, int width, int group_size,
+                     void* q, void* s, void* stream_ptr) {
+  const bool group_ok = group_size == 32 || group_size == 64 || group_size == 128 || group_size == 256;
+  if (rows < 0 || width <= 0 || width % 256 || !group_ok ||
+      (in_dtype != GG_OUT_FP32 && in_dtype != GG_OUT_BF16 && in_dtype != GG_OUT_FP16)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (rows == 0) return 0;
+  if (!x || !q || !s || !gg::aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 7)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const long long items = rows * (width / 256);
+  const long long blocks = (items + 7) / 8;
+  if (blocks > 0x7fffffffLL) return static_cast<int>(cudaErrorInvalidValue);
+  const int grid = static_cast<int>(blocks);
+  int8_t* codes = static_cast<int8_t*>(q);
+  float* scales = static_cast<float*>(s);
+  if (in_dtype == GG_OUT_FP32) {
+    gg::quantize_rows_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(x), rows,
+                                                               width, group_size, codes, scales);
+  } else if (in_dtype == GG_OUT_BF16) {
+    gg::quantize_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), rows, width, group_size, codes, scales);
+  } else {
+    gg::quantize_rows_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), rows,
+                                                                width, group_size, codes, scales);
+  }
+  return static_cast<int>(cudaGetLastError());
 }
 
 int gg_moe_combine(const void* expert_out, const void* weights, const void* inverse, void* out,

@@ -17,8 +17,10 @@
 // 128 channels; a sub-tile is one N = 256 accumulator (128 gate + 128 up columns) in TMEM.
 //   warp 8    TMA producer: per stage one box of sorted activation rows, two weight boxes
 //   warp 9    MMA issuer (tcgen05.mma kind::i8, two TMEM buffers)
-//   warps 0-7 promotion per K group, then SwiGLU; the first sub-tile's h is parked in shared
-//             memory until the second sub-tile supplies the other half of the row maximum.
+//   warp 10   scale staging (column and row scales of each K group into a shared-memory ring)
+//   warps 0-7 promotion per K group, then SwiGLU (silu by table lookup); the first sub-tile's h
+//             is parked in shared memory until the second sub-tile supplies the other half of
+//             the row maximum.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -32,6 +34,7 @@ namespace gg {
 
 struct GateUpParams {
   const float* sorted_scale;  // [S, H/256] row scales in sorted-slot order
+  const float* silu_table;    // [65536] silu of every value of the output type, by bit pattern
   const float* scale_w;       // [E, H/256, 2I]
   const int* expert_offsets;  // [E+1]
   const int* tile_expert;     // [max_tiles]
@@ -75,9 +78,14 @@ __device__ __forceinline__ bool gate_up_item(const GateUpParams& p, int item, in
   return true;
 }
 
-template <typename RoundT>
-__device__ __forceinline__ float round_through(float v) {
-  return static_cast<float>(cast_out<RoundT>(v));
+// The two 16-bit floats of a packed pair as FP32 (exact).
+template <typename T>
+__device__ __forceinline__ float2 unpack_pair(uint32_t packed) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    return make_float2(__uint_as_float(packed << 16), __uint_as_float(packed & 0xffff0000u));
+  } else {
+    return __half22float2(*reinterpret_cast<const __half2*>(&packed));
+  }
 }
 
 template <typename RoundT>
@@ -386,42 +394,33 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         // SwiGLU on the rounded gate/up values.  h[r][k] is channel (of this sub-tile's 128)
         //   split:       half*64 + (k/8)*32 + 8*((k%8)/2) + 2*quad + k%2
         //   interleaved: half*64 + (k/4)*16 + 4*(k%4) + quad
+        // gate and up are rounded to the output type first (pack_pair), so silu(gate) is a
+        // lookup by the gate's 16-bit pattern in a table built with the formula itself.
         float h[4][16];
         float amax[4];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           float row_amax = 0.0f;
+          if (p.interleaved) {
 #pragma unroll
-          for (int k0 = 0; k0 < 16; k0 += 8) {
-            float gate[8], up[8], denominator[8];
-            bool safe = true;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int k = k0 + j;
-              // split: k = b*8 + i*2 + e -> gate acc[r][b*4+i].e, up acc[r][(2+b)*4+i].e
-              const float2 gate_pair = acc[r][(k >> 3) * 4 + ((k & 7) >> 1)];
-              const float2 up_pair = acc[r][(2 + (k >> 3)) * 4 + ((k & 7) >> 1)];
-              const float gate_split = (k & 1) ? gate_pair.y : gate_pair.x;
-              const float up_split = (k & 1) ? up_pair.y : up_pair.x;
-              gate[j] = round_through<RoundT>(p.interleaved ? acc[r][k].x : gate_split);
-              up[j] = round_through<RoundT>(p.interleaved ? acc[r][k].y : up_split);
-              denominator[j] = __fadd_rn(1.0f, expf(-gate[j]));
-              safe = safe && swiglu_division_is_safe(gate[j], denominator[j]);
+            for (int k = 0; k < 16; ++k) {
+              const uint32_t pair = pack_pair<RoundT>(acc[r][k]);   // (gate, up) of one channel
+              h[r][k] = __fmul_rn(__ldg(p.silu_table + (pair & 0xffffu)), unpack_pair<RoundT>(pair).y);
             }
-            if (safe) {
+          } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float y = reciprocal_by_fma(denominator[j]);
-                h[r][k0 + j] = __fmul_rn(divide_by_fma(gate[j], denominator[j], y), up[j]);
+            for (int b = 0; b < 2; ++b) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const uint32_t gate = pack_pair<RoundT>(acc[r][b * 4 + i]);
+                const float2 up = unpack_pair<RoundT>(pack_pair<RoundT>(acc[r][(2 + b) * 4 + i]));
+                h[r][b * 8 + 2 * i] = __fmul_rn(__ldg(p.silu_table + (gate & 0xffffu)), up.x);
+                h[r][b * 8 + 2 * i + 1] = __fmul_rn(__ldg(p.silu_table + (gate >> 16)), up.y);
               }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                h[r][k0 + j] = __fmul_rn(__fdiv_rn(gate[j], denominator[j]), up[j]);
             }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) row_amax = fmaxf(row_amax, fabsf(h[r][k0 + j]));
           }
+#pragma unroll
+          for (int k = 0; k < 16; ++k) row_amax = fmaxf(row_amax, fabsf(h[r][k]));
           // The four lanes of a quad hold the row's other channels of this half.
           row_amax = fmaxf(row_amax, __shfl_xor_sync(0xffffffffu, row_amax, 1));
           row_amax = fmaxf(row_amax, __shfl_xor_sync(0xffffffffu, row_amax, 2));

@@ -210,11 +210,23 @@ moe_tiles_kernel(const int* __restrict__ offsets, int experts, int tile_rows, in
 // sorted_x[slot, :] = x[order[slot] / top_k, :] and likewise for the row scales, so that the
 // fused Gate/Up kernel can fetch whole 128-row operand tiles by TMA.  One warp per slot; a
 // row is `hidden` bytes (a multiple of 256) moved as 16-byte vectors.
+//
+// The same launch fills the SiLU table of the fused kernel: gate values reach SwiGLU rounded to
+// the 16-bit output type, so silu(gate) = div_rn(gate, 1 + exp(-gate)) has only 65536 possible
+// arguments.  Entry b holds the result for the value whose bit pattern is b, computed here with
+// exactly the operations of swiglu_value, hence bit-identical to evaluating the formula
+// (the idea of the reference's experiments/thor_interleaved_mega/exact_silu_lut.cuh:1-36).
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const int8_t* __restrict__ x, const float* __restrict__ scale_x,
                    const long long* __restrict__ order, const int* __restrict__ offsets,
                    int experts, int top_k, int hidden, int8_t* __restrict__ sorted_x,
-                   float* __restrict__ sorted_scale) {
+                   float* __restrict__ sorted_scale, float* __restrict__ silu_table,
+                   int half_output) {
+  for (int bits = blockIdx.x * 256 + threadIdx.x; bits < 65536; bits += gridDim.x * 256) {
+    const float gate = half_output ? __half2float(__ushort_as_half(static_cast<unsigned short>(bits)))
+                                   : __uint_as_float(static_cast<uint32_t>(bits) << 16);
+    silu_table[bits] = __fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate)));
+  }
   const int valid = offsets[experts];
   const int lane = threadIdx.x & 31;
   const int groups = hidden / 256;
@@ -250,31 +262,16 @@ __device__ __forceinline__ int quantize_value(float h, float scale) {
 
 // The library division carries a branch to a slow path, which keeps the compiler from
 // interleaving the long dependent chains of many divisions.  The fused Gate/Up epilogue
-// therefore divides with the classical FMA sequence, which is branch-free and, by
-// Markstein's theorems, still correctly rounded:
-//   * y0 = rcp.approx(d) is within 1 ulp, so y = fma(fma(-d, y0, 1), y0, y0) is the
-//     correctly rounded reciprocal unless d's significand is all ones;
-//   * with y = RN(1/d), q within 1 ulp of n/d and r = fma(-d, q, n) exact,
-//     fma(r, y, q) is the correctly rounded quotient.
-// Both need every intermediate to stay normal; callers test the operand ranges and fall
-// back to the library division outside them, so results always equal __fdiv_rn (a zero
-// numerator may lose its sign, which neither the scale nor the INT8 code can show).
-__device__ __forceinline__ float reciprocal_by_fma(float d) {
-  float y0;
-  asm("rcp.approx.f32 %0, %1;" : "=f"(y0) : "f"(d));
-  return __fmaf_rn(__fmaf_rn(-d, y0, 1.0f), y0, y0);
-}
+// therefore requantises (h / scale, one scale per row) with the classical FMA sequence, which
+// is branch-free and, by Markstein's theorem, still correctly rounded: with y = RN(1/d)
+// (__frcp_rn), q within 1 ulp of n/d and r = fma(-d, q, n) exact, fma(r, y, q) is the
+// correctly rounded quotient.  It needs every intermediate to stay normal; the caller tests
+// the row's range and falls back to the library division outside it, so codes always equal
+// those of __fdiv_rn.
 __device__ __forceinline__ float divide_by_fma(float n, float d, float y) {
   float q = __fmul_rn(n, y);
   q = __fmaf_rn(__fmaf_rn(-d, q, n), y, q);  // now within 1 ulp
   return __fmaf_rn(__fmaf_rn(-d, q, n), y, q);
-}
-// SwiGLU operands for which the sequence is exact: |gate| <= 64 keeps the denominator
-// 1 + exp(-gate) within [1, 2^93) and the quotient far from underflow.
-__device__ __forceinline__ bool swiglu_division_is_safe(float gate, float denominator) {
-  const float magnitude = fabsf(gate);
-  const bool numerator_ok = magnitude <= 64.0f && (magnitude >= 0x1p-60f || magnitude == 0.0f);
-  return numerator_ok && (__float_as_uint(denominator) & 0x7fffffu) != 0x7fffffu;
 }
 // Row scales for which h / scale may use the sequence with y = __frcp_rn(scale): quotients
 // of magnitude >= 1/4 then have normal residuals, and smaller ones round to 0 either way.
@@ -284,6 +281,50 @@ __device__ __forceinline__ bool quantize_division_is_safe(float row_max) {
 __device__ __forceinline__ int quantize_value_by_fma(float h, float scale, float y) {
   const float rounded = nearbyintf(divide_by_fma(h, scale, y));
   return static_cast<int>(fminf(fmaxf(rounded, -127.0f), 127.0f));
+}
+
+// Entry quantiser: symmetric per-row, per-K-group INT8 quantisation of floating rows,
+// restating quantize_rows (src/grain_gemm/kernels/moe.py:321-356):
+//   scale = div_rn(max(amax, 1e-12), 127);  q = clamp(nearbyint(div_rn(v, scale)), +-127).
+// Eight consecutive values per lane (16 bytes of BF16/FP16, 32 of FP32); a group of G values
+// is G/8 neighbouring lanes, so a warp covers 256/G groups of one row at a time.  HBM bound:
+// sizeof(InT) bytes read and one byte (+ 4/G) written per element.
+template <typename InT>
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const InT* __restrict__ x, long long rows, int width, int group,
+                     int8_t* __restrict__ q, float* __restrict__ s) {
+  const int lane = threadIdx.x & 31;
+  const int chunks = width / 256;                 // 256-value chunks per row (width % 256 == 0)
+  const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (item >= rows * chunks) return;
+  const long long row = item / chunks;
+  const int column = static_cast<int>(item - row * chunks) * 256 + lane * 8;
+  const InT* source = x + row * width + column;
+  float v[8];
+  if constexpr (sizeof(InT) == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(source);
+    const float4 b = *reinterpret_cast<const float4*>(source + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4*>(source);
+    const InT* values = reinterpret_cast<const InT*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = static_cast<float>(values[i]);
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  for (int offset = group / 16; offset > 0; offset >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+  }
+  const float scale = quantize_scale(amax);
+  uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    packed[i >> 2] |= (static_cast<uint32_t>(quantize_value(v[i], scale)) & 0xffu) << (8 * (i & 3));
+  }
+  *reinterpret_cast<uint2*>(q + row * width + column) = make_uint2(packed[0], packed[1]);
+  if ((lane & (group / 8 - 1)) == 0) s[row * (width / group) + column / group] = scale;
 }
 
 // Stand-alone SwiGLU + G256 requantisation over a [rows, 2I] gate/up matrix (the unfused

@@ -1,0 +1,92 @@
+"""The steps immediately before the two hot paths: activation quantisation and weight
+preparation, with the reference's names and conventions.
+
+* ``quantize_rows`` mirrors ``quantize_rows`` of ``src/grain_gemm/kernels/moe.py:344-356`` of
+  the reference (symmetric INT8, one FP32 scale per row and K group) and runs the CUDA kernel
+  behind ``gg_quantize_rows``.
+* ``prepare_weight`` and ``interleave_gate_up`` restate the preparation recipes of the
+  reference's ``docs/moe_ffn.md:119-133`` and ``docs/moe_interleaved.md:32-40``; they run once,
+  outside the forward pass, as plain tensor operations.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _loader
+
+
+def quantize_rows(x, group_size=256, *, rows_per_program=4):
+    """Quantize contiguous floating rows; return INT8 data and FP32 row scales.
+
+    ``x`` is ``[..., K]`` (FP32, BF16 or FP16, contiguous, on a B200), ``K`` a multiple of 256
+    and ``group_size`` one of 32, 64, 128, 256.  Returns ``(q, scales)`` with ``q`` INT8 of
+    ``x``'s shape and ``scales`` FP32 ``[..., K // group_size]``:
+    ``scale = max(|x|_group, 1e-12) / 127`` and ``q = clamp(rint(x / scale), -127, 127)``.
+    ``rows_per_program`` is accepted for signature compatibility and ignored.
+    """
+    del rows_per_program
+    if not isinstance(x, torch.Tensor) or x.dim() < 1:
+        raise ValueError("x must be a tensor with at least one dimension")
+    if x.dtype not in _loader.OUT_DTYPE:
+        raise ValueError("x must be torch.float32, torch.bfloat16 or torch.float16")
+    if group_size not in (32, 64, 128, 256):
+        raise ValueError("group_size must be one of 32, 64, 128 or 256")
+    width = x.shape[-1]
+    if width == 0 or width % 256:
+        raise ValueError("the last dimension must be a positive multiple of 256")
+    if x.device.type != "cuda":
+        raise ValueError("x must be a CUDA tensor")
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    if torch.cuda.get_device_capability(x.device) != (10, 0):
+        raise RuntimeError("this build of quantize_rows requires an NVIDIA B200 (sm_100) GPU")
+    rows = x.numel() // width
+    quantized = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scales = torch.empty((*x.shape[:-1], width // group_size), dtype=torch.float32, device=x.device)
+    if rows:
+        lib = _loader.library()
+        with torch.cuda.device(x.device):
+            _loader.check(lib.gg_quantize_rows(
+                _loader.pointer(x), _loader.OUT_DTYPE[x.dtype], rows, width, group_size,
+                _loader.pointer(quantized), _loader.pointer(scales),
+                _loader.stream_pointer(x.device)), "gg_quantize_rows")
+    return quantized, scales
+
+
+def prepare_weight(linear_weight, group_size=256):
+    """Quantise Linear-format weights ``[E, N, K]`` (or ``[N, K]``) once, outside forward.
+
+    Returns ``(q, scales)``: ``q`` is the INT8 *logical* GEMM weight ``[E, K, N]`` as a
+    transposed view of contiguous Linear storage (stride ``(N*K, 1, K)``, what ``moe_ffn`` and
+    ``int8_gemm`` take as B), ``scales`` is contiguous FP32 ``[E, K // group_size, N]``.
+    """
+    if linear_weight.dim() not in (2, 3):
+        raise ValueError("linear_weight must be [N, K] or [E, N, K]")
+    if linear_weight.device.type == "cuda" and linear_weight.shape[-1] % 256 == 0:
+        source = linear_weight if linear_weight.dtype in _loader.OUT_DTYPE else linear_weight.float()
+        q, scales = quantize_rows(source.contiguous(), group_size)
+    else:
+        k = linear_weight.shape[-1]
+        if k % group_size:
+            raise ValueError("K must be a multiple of group_size")
+        blocks = linear_weight.float().reshape(*linear_weight.shape[:-1], k // group_size, group_size)
+        scales = blocks.abs().amax(-1).clamp_min(1e-12) / 127
+        q = (blocks / scales[..., None]).round().clamp(-127, 127).to(torch.int8)
+        q = q.reshape(linear_weight.shape).contiguous()
+    return q.transpose(-2, -1), scales.transpose(-2, -1).contiguous()
+
+
+def interleave_gate_up(w_gate_up, scale_gate_up):
+    """Reorder a split ``[gate | up]`` checkpoint to ``[g0, u0, g1, u1, ...]`` once.
+
+    ``w_gate_up`` is ``[E, H, 2I]`` as a transposed view of Linear storage, ``scale_gate_up``
+    contiguous ``[E, H // 256, 2I]``; the results have the same layouts and are what
+    ``moe_ffn(..., gate_up_layout="interleaved")`` expects.
+    """
+    inter = w_gate_up.shape[-1] // 2
+    channels = torch.arange(inter, device=w_gate_up.device)
+    order = torch.stack((channels, channels + inter), dim=-1).reshape(-1)
+    linear_weight = w_gate_up.transpose(-2, -1)
+    return (linear_weight.index_select(-2, order).contiguous().transpose(-2, -1),
+            scale_gate_up.index_select(-1, order).contiguous())

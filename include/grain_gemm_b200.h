@@ -154,6 +154,17 @@ int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, 
                  void* tile_row, void* stream);
 
 /*
+ * Entry quantiser (the step before both paths): x[rows, width] of dtype in_dtype (GG_OUT_FP32,
+ * GG_OUT_BF16 or GG_OUT_FP16 name the element type), contiguous, width a multiple of 256,
+ * 16-byte aligned; writes q[rows, width] int8 and s[rows, width/group_size] fp32 with
+ * scale = max(amax, 1e-12) / 127 and q = clamp(nearbyint(x / scale), +-127), every division
+ * correctly rounded.  group_size is 32, 64, 128 or 256.
+ * Replaces quantize_rows (src/grain_gemm/kernels/moe.py:321-356).
+ */
+int gg_quantize_rows(const void* x, int in_dtype, long long rows, int width, int group_size,
+                     void* q, void* s, void* stream);
+
+/*
  * Gate/Up projection + rounding to out_dtype + SwiGLU + G256 requantisation over the sorted
  * slots: q[S,I] int8 and s[S,I/256] fp32; rows are gathered from x[T,H] by order[slot] / R.
  * w1: Linear [E,2I,H] contiguous int8; scale_w1: [E,H/256,2I] fp32.  interleaved != 0 means
@@ -162,7 +173,8 @@ int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, 
  * 32 the CUDA-core path.  gate_up_scratch must hold gg_moe_gate_up_scratch_bytes() bytes
  * (16-byte aligned): for the fused kernel the activation rows [S,H] and their scales in
  * sorted-slot order, which a small copy kernel fills first so that all operand tiles arrive
- * by TMA; for the CUDA-core path the [S,2I] gate/up matrix of out_dtype.
+ * by TMA, plus a 256 KiB table of silu over every value of out_dtype that the same kernel
+ * computes with the formula; for the CUDA-core path the [S,2I] gate/up matrix of out_dtype.
  * Replaces ragged_gemm + swiglu_quantize (src/grain_gemm/moe.py:298-304) and
  * grain_moe_gather_launch / grain_moe_interleaved_launch
  * (csrc/sm110/int8_g256_moe_gather.cu:380, int8_g256_moe_interleaved.cu:372).

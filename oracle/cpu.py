@@ -33,7 +33,7 @@ def build() -> Path:
 def _lib():
     lib = ctypes.CDLL(str(build()))
     lib.oracle_threads.restype = ctypes.c_int
-    for name in ("oracle_int8_gemm", "oracle_route", "oracle_swiglu_quantize",
+    for name in ("oracle_int8_gemm", "oracle_route", "oracle_swiglu_quantize", "oracle_quantize_rows",
                  "oracle_ragged_gemm", "oracle_combine"):
         getattr(lib, name).restype = ctypes.c_int
     return lib
@@ -124,6 +124,24 @@ def swiglu_quantize(gate_up, valid_rows=None, gate_up_layout="split"):
     if status:
         raise RuntimeError(f"oracle_swiglu_quantize failed with status {status}")
     return q, s
+
+
+def quantize_rows(x, group_size=256):
+    """Entry quantiser; restates ``quantize_rows`` (``src/grain_gemm/kernels/moe.py:321-356``).
+
+    ``x`` is ``[..., K]`` in BF16/FP16/FP32; returns INT8 data of the same shape and FP32
+    scales ``[..., K / group_size]``.
+    """
+    width = x.shape[-1]
+    values = x.float().contiguous().reshape(-1, width)
+    rows = values.shape[0]
+    q = torch.empty((rows, width), dtype=torch.int8)
+    s = torch.empty((rows, width // group_size), dtype=torch.float32)
+    status = _lib().oracle_quantize_rows(_p(values), _i64(rows), _i64(width), _i64(group_size),
+                                         _p(q), _p(s))
+    if status:
+        raise RuntimeError(f"oracle_quantize_rows failed with status {status}")
+    return q.reshape(x.shape), s.reshape(*x.shape[:-1], width // group_size)
 
 
 def ragged_gemm(a, w_linear, scale_a, scale_b, routes, output_dtype, source_is_token):

@@ -17,6 +17,7 @@
  *       range check at the ids' own width, stable sort with the invalid tail,
  *       inverse, counts, offsets, statistics)
  *   oracle_swiglu_quantize
+ *   oracle_quantize_rows
  *       src/grain_gemm/kernels/moe.py:321-328,564-601  (SwiGLU on the rounded
  *       gate/up values, per row and 256-channel group amax -> scale ->
  *       nearest-even quantisation clipped to +-127, no FMA contraction)
@@ -240,6 +241,41 @@ int oracle_swiglu_quantize(const float* gate_up, int64_t rows, int64_t valid_row
         float v = nearbyintf(h[j] / scale);
         v = v < -127.0f ? -127.0f : v > 127.0f ? 127.0f : v;
         qr[j] = (int8_t)v;
+      }
+    }
+  }
+  return 0;
+}
+
+/* ---- entry quantiser -------------------------------------------------------- */
+
+/*
+ * Symmetric per-row, per-K-group quantisation of floating rows, restating
+ * _symmetric_quantize_row_block / quantize_rows (src/grain_gemm/kernels/moe.py:321-356):
+ *   scale = div_rn(max(amax, 1e-12), 127);  q = clamp(nearbyint(div_rn(v, scale)), -127, 127).
+ * x: [rows, width] FP32 (the caller converts BF16/FP16 exactly); q: [rows, width] int8;
+ * s: [rows, width / group] FP32.
+ */
+int oracle_quantize_rows(const float* x, int64_t rows, int64_t width, int64_t group, int8_t* q,
+                         float* s) {
+  if (group <= 0 || width % group) return 1;
+  int64_t groups = width / group;
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    for (int64_t g = 0; g < groups; ++g) {
+      const float* v = x + r * width + g * group;
+      float amax = 0.0f;
+      for (int64_t j = 0; j < group; ++j) {
+        float a = fabsf(v[j]);
+        if (a > amax || a != a) amax = a;
+      }
+      float m = amax > 1.0e-12f ? amax : 1.0e-12f;
+      float scale = m / 127.0f;
+      s[r * groups + g] = scale;
+      for (int64_t j = 0; j < group; ++j) {
+        float t = nearbyintf(v[j] / scale);
+        t = t < -127.0f ? -127.0f : t > 127.0f ? 127.0f : t;
+        q[r * width + g * group + j] = (int8_t)t;
       }
     }
   }

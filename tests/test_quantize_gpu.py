@@ -1,0 +1,90 @@
+"""Entry quantiser and weight preparation on the GPU, through the C ABI, against the oracle."""
+
+import pytest
+import torch
+
+from oracle import cpu as oracle
+from tests.conftest import load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def quantize():
+    from grain_gemm_b200 import quantize as module
+    return module
+
+
+def test_reference_vectors(quantize):
+    case = load_golden("quantizer_known")
+    q, s = quantize.quantize_rows(case["x"].cuda())
+    assert torch.equal(q.cpu(), case["q"])
+    assert torch.equal(s.cpu(), case["s"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("group", [32, 64, 128, 256])
+def test_random_rows_bit_exact(quantize, dtype, group):
+    gen = torch.Generator().manual_seed(group)
+    x = (torch.randn((37, 3, 1024), generator=gen) * 3).to(dtype)
+    x[0, 0, :256] = 0                         # all-zero group: scale 1e-12 / 127, codes 0
+    x[1, 1, 5] = 1.0e30 if dtype != torch.float16 else 6.0e4
+    x[2, 2, 256:512] = 1.0e-30 if dtype != torch.float16 else 6.0e-8
+    q, s = quantize.quantize_rows(x.cuda(), group)
+    expected_q, expected_s = oracle.quantize_rows(x, group)
+    assert q.shape == x.shape and s.shape == (37, 3, 1024 // group)
+    assert torch.equal(s.cpu(), expected_s)
+    assert torch.equal(q.cpu(), expected_q)
+    assert int(q.abs().max()) == 127
+
+
+def test_ties_round_to_even_and_clamp(quantize):
+    x = torch.zeros((1, 256))
+    x[0, 0] = 127.0                            # scale exactly 1
+    x[0, 1:7] = torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, -2.5])
+    q, s = quantize.quantize_rows(x.cuda())
+    assert s.item() == 1.0
+    assert q[0, :7].tolist() == [127, 0, 2, 2, 0, -2, -2]
+
+
+def test_empty_and_argument_errors(quantize):
+    q, s = quantize.quantize_rows(torch.empty((0, 512), device="cuda"))
+    assert q.shape == (0, 512) and s.shape == (0, 2)
+    with pytest.raises(ValueError, match="multiple of 256"):
+        quantize.quantize_rows(torch.zeros((4, 100), device="cuda"))
+    with pytest.raises(ValueError, match="group_size"):
+        quantize.quantize_rows(torch.zeros((4, 256), device="cuda"), 48)
+    with pytest.raises(ValueError, match="contiguous"):
+        quantize.quantize_rows(torch.zeros((256, 4), device="cuda").t())
+    with pytest.raises(ValueError, match="float"):
+        quantize.quantize_rows(torch.zeros((4, 256), dtype=torch.int8, device="cuda"))
+
+
+def test_quantised_rows_feed_the_gemm(quantize):
+    """Quantise activations and weights with the helpers and run int8_gemm on the result."""
+    from grain_gemm_b200 import int8_gemm
+    gen = torch.Generator().manual_seed(9)
+    x = torch.randn((64, 512), generator=gen)
+    weight = torch.randn((128, 512), generator=gen) / 512 ** 0.5      # Linear [N, K]
+    qx, sx = quantize.quantize_rows(x.cuda())
+    qw, sw = quantize.prepare_weight(weight.cuda())
+    assert qw.shape == (512, 128) and qw.stride() == (1, 512) and sw.shape == (2, 128)
+    out = int8_gemm(qx, qw, sx, sw, output_dtype=torch.float32)
+    expected = oracle.int8_gemm(qx.cpu(), qw.cpu(), sx.cpu(), sw.cpu(), 256, torch.float32)
+    assert torch.equal(out.cpu(), expected)
+    torch.testing.assert_close(out.cpu(), x @ weight.t(), rtol=0.05, atol=0.05)
+
+
+def test_prepare_weight_and_interleave(quantize):
+    gen = torch.Generator().manual_seed(4)
+    weight = torch.randn((3, 512, 256), generator=gen)                # [E, 2I, H]
+    q, s = quantize.prepare_weight(weight.cuda())
+    q_cpu, s_cpu = quantize.prepare_weight(weight)
+    assert q.shape == (3, 256, 512) and q.stride() == (512 * 256, 1, 256)
+    assert s.shape == (3, 1, 512) and s.is_contiguous()
+    assert torch.equal(q.cpu(), q_cpu) and torch.equal(s.cpu(), s_cpu)
+    qi, si = quantize.interleave_gate_up(q, s)
+    inter = 256
+    assert qi.stride() == q.stride()
+    assert torch.equal(qi[..., 0::2], q[..., :inter]) and torch.equal(qi[..., 1::2], q[..., inter:])
+    assert torch.equal(si[..., 0::2], s[..., :inter]) and torch.equal(si[..., 1::2], s[..., inter:])
