@@ -139,103 +139,6 @@ __device__ __forceinline__ TileWork decode_tile(const GemmTcParams& p, int tile)
   return w;
 }
 
-template <typename OutT>
-__device__ __forceinline__ void store_row_chunk(OutT* dst, const float* v, int count);
-
-// Stores up to 8 consecutive outputs; `vector` promises 16-byte alignment and count == 8.
-template <>
-__device__ __forceinline__ void store_row_chunk<float>(float* dst, const float* v, int count) {
-  for (int i = 0; i < count; ++i) dst[i] = v[i];
-}
-template <>
-__device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* dst, const float* v,
-                                                               int count) {
-  for (int i = 0; i < count; ++i) dst[i] = __float2bfloat16_rn(v[i]);
-}
-template <>
-__device__ __forceinline__ void store_row_chunk<__half>(__half* dst, const float* v, int count) {
-  for (int i = 0; i < count; ++i) dst[i] = __float2half_rn(v[i]);
-}
-
-template <typename OutT>
-__device__ __forceinline__ OutT cast_out_tc(float v) {
-  if constexpr (sizeof(OutT) == 4) return v;
-  else if constexpr (std::is_same<OutT, __nv_bfloat16>::value) return __float2bfloat16_rn(v);
-  else return __float2half_rn(v);
-}
-
-template <typename OutT>
-__device__ __forceinline__ void store_row_vector8(OutT* dst, const float* v) {
-  if constexpr (sizeof(OutT) == 4) {
-    float4* d = reinterpret_cast<float4*>(dst);
-    d[0] = make_float4(v[0], v[1], v[2], v[3]);
-    d[1] = make_float4(v[4], v[5], v[6], v[7]);
-  } else if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
-    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]);
-    __nv_bfloat162 p1 = __floats2bfloat162_rn(v[2], v[3]);
-    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]);
-    __nv_bfloat162 p3 = __floats2bfloat162_rn(v[6], v[7]);
-    uint4 packed;
-    packed.x = *reinterpret_cast<uint32_t*>(&p0);
-    packed.y = *reinterpret_cast<uint32_t*>(&p1);
-    packed.z = *reinterpret_cast<uint32_t*>(&p2);
-    packed.w = *reinterpret_cast<uint32_t*>(&p3);
-    *reinterpret_cast<uint4*>(dst) = packed;
-  } else {
-    __half2 p0 = __floats2half2_rn(v[0], v[1]);
-    __half2 p1 = __floats2half2_rn(v[2], v[3]);
-    __half2 p2 = __floats2half2_rn(v[4], v[5]);
-    __half2 p3 = __floats2half2_rn(v[6], v[7]);
-    uint4 packed;
-    packed.x = *reinterpret_cast<uint32_t*>(&p0);
-    packed.y = *reinterpret_cast<uint32_t*>(&p1);
-    packed.z = *reinterpret_cast<uint32_t*>(&p2);
-    packed.w = *reinterpret_cast<uint32_t*>(&p3);
-    *reinterpret_cast<uint4*>(dst) = packed;
-  }
-}
-
-// One promotion step over kWidth drained columns: acc = fmaf(float(partial), sa*sb, acc), two
-// columns per packed FP32 instruction (IEEE round-to-nearest per lane, bit-identical to the
-// scalar mul.rn / fma.rn).  GG_SCALAR_PROMOTE selects the scalar form for comparison.
-template <int kWidth>
-__device__ __forceinline__ void promote(const uint32_t (&partial)[kWidth], float sa,
-                                        const float* __restrict__ sb_smem, float2* acc) {
-#pragma unroll
-  for (int j = 0; j < kWidth; j += 4) {
-    const float4 sb = *reinterpret_cast<const float4*>(sb_smem + j);
-#ifdef GG_CONVERT_I2F
-    const float2 p01 = make_float2(__int2float_rn(static_cast<int>(partial[j + 0])),
-                                   __int2float_rn(static_cast<int>(partial[j + 1])));
-    const float2 p23 = make_float2(__int2float_rn(static_cast<int>(partial[j + 2])),
-                                   __int2float_rn(static_cast<int>(partial[j + 3])));
-#else
-    // Exact INT32 -> FP32 for |partial| <= 2^22 (a 256-long dot of INT8 products) without the
-    // conversion unit: the integer is added to the bit pattern of 1.5 * 2^23, whose unit in
-    // the last place is 1, then 1.5 * 2^23 is subtracted again; both steps are exact.
-    const float2 bias = make_float2(-12582912.0f, -12582912.0f);
-    const float2 p01 = __fadd2_rn(
-        make_float2(__uint_as_float(partial[j + 0] + 0x4B400000u),
-                    __uint_as_float(partial[j + 1] + 0x4B400000u)), bias);
-    const float2 p23 = __fadd2_rn(
-        make_float2(__uint_as_float(partial[j + 2] + 0x4B400000u),
-                    __uint_as_float(partial[j + 3] + 0x4B400000u)), bias);
-#endif
-#ifdef GG_SCALAR_PROMOTE
-    acc[j / 2].x = __fmaf_rn(p01.x, __fmul_rn(sa, sb.x), acc[j / 2].x);
-    acc[j / 2].y = __fmaf_rn(p01.y, __fmul_rn(sa, sb.y), acc[j / 2].y);
-    acc[j / 2 + 1].x = __fmaf_rn(p23.x, __fmul_rn(sa, sb.z), acc[j / 2 + 1].x);
-    acc[j / 2 + 1].y = __fmaf_rn(p23.y, __fmul_rn(sa, sb.w), acc[j / 2 + 1].y);
-#else
-    const float2 sa2 = make_float2(sa, sa);
-    const float2 s01 = __fmul2_rn(sa2, make_float2(sb.x, sb.y));
-    const float2 s23 = __fmul2_rn(sa2, make_float2(sb.z, sb.w));
-    acc[j / 2] = __ffma2_rn(p01, s01, acc[j / 2]);
-    acc[j / 2 + 1] = __ffma2_rn(p23, s23, acc[j / 2 + 1]);
-#endif
-  }
-}
-
 // Promotion of one 16-row x 32-column fragment (tmem_ld_16x256b_x4 layout): this thread holds
 // rows r and r+8 and column pairs 8i+2q, 8i+2q+1.  `sb` are its four column-scale pairs, read
 // once per 32-column block and used for both 16-row halves.
@@ -252,22 +155,6 @@ __device__ __forceinline__ void promote_fragment(const uint32_t (&partial)[16], 
                                     __int2float_rn(static_cast<int>(partial[4 * i + 3])));
     acc_low[i] = __ffma2_rn(low, __fmul2_rn(sa_low2, sb[i]), acc_low[i]);
     acc_high[i] = __ffma2_rn(high, __fmul2_rn(sa_high2, sb[i]), acc_high[i]);
-  }
-}
-
-template <typename OutT>
-__device__ __forceinline__ void store_pair(OutT* dst, float2 v, bool both, bool aligned) {
-  if (both && aligned) {
-    if constexpr (sizeof(OutT) == 4) {
-      *reinterpret_cast<float2*>(dst) = v;
-    } else if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
-      *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v.x, v.y);
-    } else {
-      *reinterpret_cast<__half2*>(dst) = __floats2half2_rn(v.x, v.y);
-    }
-  } else {
-    dst[0] = cast_out_tc<OutT>(v.x);
-    if (both) dst[1] = cast_out_tc<OutT>(v.y);
   }
 }
 
@@ -307,7 +194,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const GemmTcParams p) {
   using Shape = GemmTcShape<kCtaGroup, BN, kStages, kPromoWarps, kARows>;
   constexpr int kNC = Shape::kColumnsPerThread;   // columns owned by one promotion thread
-  constexpr int kDW = Shape::kDrainWidth;
   constexpr int kProducerWarp = kPromoWarps, kMmaWarp = kPromoWarps + 1;
   constexpr int kScaleWarp = kPromoWarps + 2;
 

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels use:
-// mbarrier, TMA tiled loads, tcgen05 (alloc / mma / commit / ld) and packed FP32 math.
+// mbarrier, TMA tiled loads, tcgen05 (alloc / mma / commit / ld), register reallocation and barriers.
 // Every wait is bounded: a wait that runs out returns false and the caller unwinds.
 #pragma once
 
@@ -19,8 +19,6 @@ enum WaitSite : unsigned int {
   kSiteMmaTmemEmpty = 3,
   kSiteEpilogueTmemFull = 4,
   kSiteDrain = 5,
-  kSiteGatherEmpty = 6,
-  kSiteEpilogueStash = 7,
   kSiteScaleEmpty = 8,
   kSiteScaleFull = 9,
 };
@@ -88,9 +86,6 @@ __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -246,19 +241,6 @@ __device__ __forceinline__ void tcgen05_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes
-// with the 128-byte swizzle (what a TMA load with SWIZZLE_128B writes): 8-row atoms of
-// 1024 bytes, consecutive atoms 1024 bytes apart.  The tile base must be 1024-byte aligned;
-// advancing along K inside the 128-byte row adds the byte offset to the start address.
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
-  uint64_t desc = 0;
-  desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);          // start address
-  desc |= static_cast<uint64_t>(1) << 16;                               // leading byte offset (unused)
-  desc |= static_cast<uint64_t>(1024 >> 4) << 32;                       // stride byte offset
-  desc |= static_cast<uint64_t>(1) << 46;                               // descriptor version (sm_100)
-  desc |= static_cast<uint64_t>(2) << 61;                               // SWIZZLE_128B
-  return desc;
-}
 
 // Instruction descriptor for kind::i8: signed 8-bit A and B, both K-major, INT32 accumulate.
 __host__ __device__ constexpr uint32_t make_idesc_i8(int m, int n) {
@@ -337,17 +319,6 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
       : "memory");
 }
 
-// Same for 16 columns.
-__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
 
 // 16 TMEM lanes x 32 columns in the matrix-fragment layout: with q = lane % 4 and
 // r = lane / 4, register 4i+0/4i+1 hold row r, columns 8i+2q and 8i+2q+1; registers 4i+2/4i+3
@@ -363,12 +334,6 @@ __device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)
       : "memory");
 }
 
-template <int kWidth>
-__device__ __forceinline__ void tmem_ld_columns(uint32_t taddr, uint32_t (&r)[kWidth]) {
-  static_assert(kWidth == 16 || kWidth == 32, "unsupported drain width");
-  if constexpr (kWidth == 32) tmem_ld_32x32b_x32(taddr, r);
-  else tmem_ld_32x32b_x16(taddr, r);
-}
 
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -393,37 +358,6 @@ __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
                    : "memory");
-}
-
-// Packed FP32 pair arithmetic (two independent IEEE round-to-nearest operations per
-// instruction).  Results are bit-identical to the scalar mul.rn / fma.rn.
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t"
-      ".reg .b64 ra, rb, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\t"
-      "mov.b64 rb, {%4, %5};\n\t"
-      "mul.rn.f32x2 rd, ra, rb;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t"
-      "}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-  float2 d;
-  asm("{\n\t"
-      ".reg .b64 ra, rb, rc, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\t"
-      "mov.b64 rb, {%4, %5};\n\t"
-      "mov.b64 rc, {%6, %7};\n\t"
-      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t"
-      "}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-  return d;
 }
 
 }  // namespace gg
