@@ -16,6 +16,7 @@ Intermediates use the ragged sorted-slot layout (``[S, I]`` INT8 + ``[S, I/256]`
 
 from __future__ import annotations
 
+import threading
 from dataclasses import dataclass
 
 import torch
@@ -254,6 +255,30 @@ def combine(expert_output, topk_weights, routes, *, output_dtype=torch.bfloat16)
     return out
 
 
+_HOST = threading.local()
+
+
+def _statistics_readback(statistics):
+    """Start an asynchronous copy of the routing statistics to pinned host memory.
+
+    Returns ``(host_tensor, event)``; the event completes as soon as routing has run, so a
+    caller that first launches the remaining stages and only then waits on it never leaves the
+    GPU idle.  One pinned buffer per thread and device is reused: a call's readback is consumed
+    before the same thread can start another call.
+    """
+    buffers = getattr(_HOST, "buffers", None)
+    if buffers is None:
+        buffers = _HOST.buffers = {}
+    key = statistics.device.index
+    if key not in buffers:
+        buffers[key] = torch.empty((3,), dtype=torch.int32, pin_memory=True)
+    host = buffers[key]
+    host.copy_(statistics, non_blocking=True)
+    event = torch.cuda.Event()
+    event.record()
+    return host, event
+
+
 def _tensor_core_ready(*tensors):
     return all(t.data_ptr() % 16 == 0 for t in tensors)
 
@@ -276,7 +301,8 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
     ``amax.clamp_min(1e-12)/127``, nearest-even rounding and clipping to [-127,127].
 
     Eager calls read three integers back to reject unmasked ids outside ``[0,E)`` with a
-    ``ValueError``; under CUDA-graph capture that check is skipped.  ``variant`` is
+    ``ValueError`` (the copy overlaps the remaining stages; the call returns or raises once
+    routing has run); under CUDA-graph capture that check is skipped.  ``variant`` is
     ``'auto'``, ``'tensor_core'`` or ``'cuda_core'`` (tests and benchmarks).
     """
     tokens, hidden, intermediate, experts, top_k = _validate(
@@ -297,16 +323,20 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
         tile_rows = (CUDA_CORE_TILE_ROWS if variant == "cuda_core" or not aligned
                      else TENSOR_CORE_TILE_ROWS)
         routes = prepare_routes(topk_ids, experts, token_mask, tile_rows=tile_rows)
-        if not capturing:
-            invalid, maximum, total = routes.statistics.cpu().tolist()
-            if invalid:
-                raise ValueError("unmasked topk_ids must be in [0, E)")
-            if total == 0:
-                return torch.zeros(hidden_states.shape, device=hidden_states.device,
-                                   dtype=output_dtype)
+        # The check for unmasked ids outside [0, E) reads three integers back.  Its copy is
+        # started now and awaited after the remaining stages are in the stream (they are safe
+        # for any ids: invalid assignments sort to the ignored tail), so the GPU never waits
+        # for the host between routing and Gate/Up.
+        readback = None if capturing else _statistics_readback(routes.statistics)
         qh, sh = gate_up_swiglu_quantize(
             hidden_states, scale_x, w1_linear, scale_gate_up, routes,
             output_dtype=output_dtype, gate_up_layout=gate_up_layout)
         expert_output = down_projection(qh, sh, w2_linear, scale_down, routes,
                                         output_dtype=output_dtype)
-        return combine(expert_output, topk_weights, routes, output_dtype=output_dtype)
+        out = combine(expert_output, topk_weights, routes, output_dtype=output_dtype)
+        if readback is not None:
+            host, event = readback
+            event.synchronize()
+            if int(host[0]):
+                raise ValueError("unmasked topk_ids must be in [0, E)")
+        return out

@@ -209,6 +209,15 @@ def test_masked_rows_may_hold_nan_and_out_of_range_ids(moe):
     torch.testing.assert_close(actual.float(), expected.float(), rtol=RTOL, atol=ATOL)
 
 
+@pytest.mark.parametrize("variant", ["cuda_core", "tensor_core"])
+def test_all_tokens_masked_returns_zeros(moe, variant):
+    case = make_case(70, 512, 256, 4, 2)
+    case["token_mask"] = torch.zeros((70,), dtype=torch.bool)
+    case["scale_x"][:] = float("nan")
+    actual = moe.moe_ffn(**to_cuda(case), variant=variant).cpu()
+    assert actual.shape == (70, 512) and actual.abs().sum() == 0
+
+
 def test_unmasked_invalid_ids_raise(moe):
     case = make_case(8, 256, 256, 4, 2)
     case["topk_ids"][3, 1] = 4
