@@ -4,14 +4,16 @@ The reference has no distributed code; this module adds the partitioning its ope
 allow without changing their arithmetic:
 
 * ``moe_ffn_expert_parallel``: experts are split contiguously over the ranks (expert ``e``
-  lives on rank ``e // (E / W)``), tokens are sharded per rank.  One exchange step each way:
-  every rank sorts its assignments by destination rank (the routing kernel with the rank as
-  the key), sends the INT8 rows, their scales and the local expert index with NCCL
-  ``all_to_all_single``, runs stages 1-3 of the FFN on what it received, sends the expert
-  outputs back the same way and combines them at home in slot order.  Each assignment is
-  computed from the same inputs by the same kernels as on one GPU, and the combine adds the
-  slots in the same order, so the result equals the single-GPU result bit for bit.
-  Remote rows always land in local memory first; kernels only ever read local memory.
+  lives on rank ``e // (E / W)``), tokens are sharded per rank.  One exchange step each way.
+  Out: every rank sends each token row, its scales and its per-slot local expert indices once
+  to every rank that holds at least one of the token's experts (the (token, rank) pairs are
+  sorted by rank with the routing kernel) with NCCL ``all_to_all_single``; the receiving rank
+  runs stages 1-3 of the FFN on those tokens with its own experts.  Back: the expert outputs
+  travel per assignment, grouped by home rank in (token, slot) order, and the home rank
+  combines them in slot order.  Each assignment is computed from the same inputs by the same
+  kernels as on one GPU, and the combine adds the slots in the same order, so the result
+  equals the single-GPU result bit for bit.  Remote rows always land in local memory first;
+  kernels only ever read local memory.
 * ``int8_gemm_n_sharded``: a rank owns a block of B's columns (and of ``scale_b`` and C);
   A and ``scale_a`` are replicated.  Column blocks are independent, so there is no
   data-path collective; ``gather=True`` all-gathers C when the caller wants it whole.
@@ -34,16 +36,22 @@ class CudaStages:
         from . import moe
         return moe.prepare_routes(keys, num_keys, token_mask, tile_rows=0)
 
-    def expert_ffn(self, x, scale_x, expert_ids, w_gate_up, w_down, scale_gate_up, scale_down,
-                   output_dtype, gate_up_layout):
-        """FFN of every received row through its (local) expert; output in received order."""
+    def expert_ffn(self, x, scale_x, expert_ids, valid, w_gate_up, w_down, scale_gate_up,
+                   scale_down, output_dtype, gate_up_layout):
+        """FFN of the received tokens through this rank's experts.
+
+        ``x [m, H]`` / ``scale_x`` are the received token rows, ``expert_ids [m, R]`` their
+        local expert indices with ``E_local`` marking the slots that belong to other ranks.
+        Returns the expert outputs of the ``valid`` real assignments as ``[valid, H]`` in
+        flattened ``(token, slot)`` order, which is the order the home ranks expect.
+        """
         from . import moe
-        rows = x.shape[0]
+        tokens, top_k = expert_ids.shape
         experts = w_gate_up.shape[0]
-        if rows == 0:
+        if tokens == 0 or valid == 0:
             return torch.empty((0, x.shape[1]), dtype=output_dtype, device=x.device)
         aligned = all(t.data_ptr() % 16 == 0 for t in (x, w_gate_up, w_down))
-        routes = moe.prepare_routes(expert_ids.reshape(rows, 1), experts, None,
+        routes = moe.prepare_routes(expert_ids, experts, None,
                                     tile_rows=moe.TENSOR_CORE_TILE_ROWS if aligned
                                     else moe.CUDA_CORE_TILE_ROWS)
         qh, sh = moe.gate_up_swiglu_quantize(
@@ -51,9 +59,10 @@ class CudaStages:
             output_dtype=output_dtype, gate_up_layout=gate_up_layout)
         sorted_out = moe.down_projection(qh, sh, w_down.transpose(-2, -1), scale_down, routes,
                                          output_dtype=output_dtype)
-        # Back to received order: a top-1 combine with unit weights is an exact row gather.
-        ones = torch.ones((rows, 1), dtype=torch.float32, device=x.device)
-        return moe.combine(sorted_out, ones, routes, output_dtype=output_dtype)
+        # Real assignments in flattened order: a stable sort with one key puts them first.
+        foreign = (expert_ids >= experts).reshape(-1, 1).to(torch.int32)
+        flattened = moe.prepare_routes(foreign, 1, None, tile_rows=0).order[:valid]
+        return sorted_out.index_select(0, routes.inverse.index_select(0, flattened).long())
 
     def combine(self, rows, topk_weights, routes, output_dtype):
         from . import moe
@@ -92,44 +101,63 @@ def moe_ffn_expert_parallel(hidden_states, w_gate_up, w_down, topk_weights, topk
     top_k = topk_ids.shape[1]
     device = hidden_states.device
 
-    # 1. Sort the local assignments by destination rank.  Out-of-range ids keep a key outside
-    #    [0, W) so that the routing statistics count them exactly as on one GPU.
+    # 1. Sort the local assignments by destination rank (for the way back), and the
+    #    (token, rank) pairs a token has at least one expert on (for the way out): a token row
+    #    crosses the link once per destination rank, not once per assignment.  Out-of-range ids
+    #    keep a key outside [0, W) so that the routing statistics count them as on one GPU.
     in_range = (topk_ids >= 0) & (topk_ids < num_experts)
     destination = torch.where(in_range, topk_ids // local_experts,
                               torch.full_like(topk_ids, world))
     routes = stages.route(destination.contiguous(), world, token_mask)
-    counts_and_invalid = torch.cat([routes.counts.to(torch.int64),
-                                    routes.statistics[:1].to(torch.int64)])
+    reachable = destination if token_mask is None else torch.where(
+        token_mask.reshape(-1, 1).to(torch.bool), destination, torch.full_like(destination, world))
+    member = torch.zeros((tokens, world + 1), dtype=torch.bool, device=device)
+    member.scatter_(1, reachable.long(), True)
+    ranks = torch.arange(world, dtype=topk_ids.dtype, device=device).expand(tokens, world)
+    pair_keys = torch.where(member[:, :world], ranks, torch.full_like(ranks, world))
+    pairs = stages.route(pair_keys.contiguous(), world, None)
 
-    # 2. Announce per-destination counts (and whether any rank saw an invalid id).
-    announced = torch.empty((world, world + 1), dtype=torch.int64, device=device)
-    dist.all_gather_into_tensor(announced, counts_and_invalid.reshape(1, -1), group=group)
+    # 2. Announce per-destination token and assignment counts (and any invalid id).
+    counts = torch.cat([pairs.counts.to(torch.int64), routes.counts.to(torch.int64),
+                        routes.statistics[:1].to(torch.int64)])
+    announced = torch.empty((world, 2 * world + 1), dtype=torch.int64, device=device)
+    dist.all_gather_into_tensor(announced, counts.reshape(1, -1), group=group)
     announced = announced.cpu()
-    if int(announced[:, world].sum()):
+    if int(announced[:, 2 * world].sum()):
         raise ValueError("unmasked topk_ids must be in [0, E)")
     rank = dist.get_rank(group)
-    send_counts = announced[rank, :world].tolist()
-    recv_counts = announced[:, rank].tolist()
-    valid = int(sum(send_counts))
+    send_tokens = announced[rank, :world].tolist()
+    recv_tokens = announced[:, rank].tolist()
+    send_assignments = announced[rank, world:2 * world].tolist()
+    recv_assignments = announced[:, world + rank].tolist()
+    sent_tokens = int(sum(send_tokens))
+    valid = int(sum(send_assignments))
 
-    # 3. Dispatch: rows, scales and local expert index, grouped by destination rank.
-    assignment = routes.order[:valid]
-    source_token = assignment // top_k
+    # 3. Dispatch: token rows, their scales and, per token, the local expert index of each of
+    #    its slots on the destination rank (E_local marks slots that live elsewhere).
+    pair = pairs.order[:sent_tokens]
+    source_token = pair // world
+    pair_rank = (pair % world).reshape(-1, 1)
     send_x = hidden_states.index_select(0, source_token)
     send_scale = scale_x.index_select(0, source_token)
-    send_expert = (topk_ids.reshape(-1).index_select(0, assignment) % local_experts).to(torch.int32)
-    recv_x = _all_to_all_rows(send_x, send_counts, recv_counts, group)
-    recv_scale = _all_to_all_rows(send_scale, send_counts, recv_counts, group)
-    recv_expert = _all_to_all_rows(send_expert, send_counts, recv_counts, group)
-    if recv_x.shape[0] != sum(recv_counts) or recv_expert.shape[0] != recv_x.shape[0]:
+    token_ids = topk_ids.index_select(0, source_token)
+    on_rank = reachable.index_select(0, source_token) == pair_rank
+    send_expert = torch.where(on_rank, token_ids - pair_rank * local_experts,
+                              torch.full_like(token_ids, local_experts)).to(torch.int32)
+    recv_x = _all_to_all_rows(send_x, send_tokens, recv_tokens, group)
+    recv_scale = _all_to_all_rows(send_scale, send_tokens, recv_tokens, group)
+    recv_expert = _all_to_all_rows(send_expert, send_tokens, recv_tokens, group)
+    if recv_x.shape[0] != sum(recv_tokens) or recv_expert.shape[0] != recv_x.shape[0]:
         raise RuntimeError("expert-parallel dispatch delivered a different number of rows than announced")
 
-    # 4. Local experts on the received rows (stages 1-3 of the FFN), in received order.
-    computed = stages.expert_ffn(recv_x, recv_scale, recv_expert, w_gate_up, w_down,
-                                 scale_gate_up, scale_down, output_dtype, gate_up_layout)
+    # 4. Local experts on the received tokens (stages 1-3 of the FFN); outputs of the real
+    #    assignments in (source rank, token, slot) order.
+    computed = stages.expert_ffn(recv_x, recv_scale, recv_expert, int(sum(recv_assignments)),
+                                 w_gate_up, w_down, scale_gate_up, scale_down, output_dtype,
+                                 gate_up_layout)
 
     # 5. Return the expert outputs to the ranks that own the tokens, then combine at home.
-    returned = _all_to_all_rows(computed, recv_counts, send_counts, group)
+    returned = _all_to_all_rows(computed, recv_assignments, send_assignments, group)
     if returned.shape[0] != valid:
         raise RuntimeError("expert-parallel combine delivered a different number of rows than sent")
     if valid == 0:

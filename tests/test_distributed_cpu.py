@@ -1,8 +1,8 @@
 """Expert-parallel exchange logic on CPU ranks (gloo, world size 2).
 
 The local stages are the CPU oracle here, so these tests cover the host-side logic of
-``grain_gemm_b200.distributed``: destination sorting, count exchange, dispatch, return and
-the home combine.  The expert-parallel result must equal the single-process result bit for
+``grain_gemm_b200.distributed``: destination sorting of assignments and of (token, rank)
+pairs, count exchange, token-level dispatch, per-assignment return and the home combine.  The expert-parallel result must equal the single-process result bit for
 bit, and a bad id on one rank must raise on every rank before anything is exchanged.
 """
 
@@ -29,15 +29,18 @@ class OracleStages:
     def route(self, keys, num_keys, token_mask=None):
         return oracle.route(keys, num_keys, token_mask)
 
-    def expert_ffn(self, x, scale_x, expert_ids, w_gate_up, w_down, scale_gate_up, scale_down,
-                   output_dtype, gate_up_layout):
-        rows = x.shape[0]
-        if rows == 0:
+    def expert_ffn(self, x, scale_x, expert_ids, valid, w_gate_up, w_down, scale_gate_up,
+                   scale_down, output_dtype, gate_up_layout):
+        experts = w_gate_up.shape[0]
+        token, slot = torch.nonzero(expert_ids < experts, as_tuple=True)   # flattened order
+        assert token.numel() == valid
+        if valid == 0:
             return torch.empty((0, x.shape[1]), dtype=output_dtype)
-        return oracle.moe_ffn(x, w_gate_up, w_down, torch.ones((rows, 1)),
-                              expert_ids.reshape(rows, 1), scale_x=scale_x,
-                              scale_gate_up=scale_gate_up, scale_down=scale_down,
-                              output_dtype=output_dtype, gate_up_layout=gate_up_layout)
+        return oracle.moe_ffn(x[token], w_gate_up, w_down, torch.ones((valid, 1)),
+                              expert_ids[token, slot].reshape(valid, 1).long(),
+                              scale_x=scale_x[token], scale_gate_up=scale_gate_up,
+                              scale_down=scale_down, output_dtype=output_dtype,
+                              gate_up_layout=gate_up_layout)
 
     def combine(self, rows, topk_weights, routes, output_dtype):
         return oracle.combine(rows, topk_weights, routes, output_dtype)
