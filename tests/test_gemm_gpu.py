@@ -95,6 +95,27 @@ def test_random_linear_layout_bit_exact(gg, variant, g):
         assert torch.equal(actual, expected), (variant, g, dtype)
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_random_shapes_dtypes_and_variants_bit_exact(gg, seed):
+    """Seeded sweep over ragged M/N/K, all group sizes, output types and variants: the C tile
+    leaves through a quad exchange and 16-byte stores, so N tails, unaligned row pitches
+    (N not a multiple of 8) and FP32 output each take their own path."""
+    import random
+    rng = random.Random(seed)
+    for _ in range(12):
+        m = rng.choice([1, 3, 17, 100, 128, 129, 255, 300, 513])
+        n = rng.choice([8, 24, 72, 136, 200, 256, 264, 520])
+        g = rng.choice([32, 64, 128, 256])
+        k = rng.choice([16, 48, 128, 272, 512, 768, 1040])
+        dtype = rng.choice([torch.float32, torch.bfloat16, torch.float16])
+        variant = rng.choice(ALL_VARIANTS + ["auto"])
+        a, b, sa, sb = linear_case(m, n, k, g, seed * 100 + m + n + k, scale="lognormal")
+        expected = oracle.int8_gemm(a, b, sa, sb, g, dtype)
+        out = torch.empty((m, n), dtype=dtype, device="cuda")
+        gg.launch(a.cuda(), b.cuda(), sa.cuda(), sb.cuda(), out, g, variant)
+        assert torch.equal(out.cpu(), expected), (m, n, k, g, dtype, variant)
+
+
 @pytest.mark.parametrize("variant", TC_VARIANTS)
 def test_int32_group_partials_bit_exact_on_tensor_cores(gg, variant):
     """Unit scales on one group at a time expose float(partial) exactly (|p| <= 2^22)."""
