@@ -4,8 +4,9 @@ Headline workload (N = 1): the W8A8 G256 GEMM at M = N = K = 8192 with BF16 outp
 (seeded synthetic INT8 operands uniform in [-127, 127], lognormal FP32 scales), metric
 ``g256_gemm_effective_int8_tops`` = 2*M*N*K / t.  A step is one GEMM over inputs resident in
 HBM.  ``e2e`` is the same metric through the public ``int8_gemm`` call with HOST (pinned)
-operands: host-to-device copies of A, B and the scales and the device-to-host read of C are
-inside the timed region.
+operands: every step's host-to-device copies of A, B and the scales and the device-to-host
+read of C are inside the timed region; consecutive steps are pipelined over a copy-in, a
+compute and a copy-out stream (two device buffer sets), so the rate is that of the slowest leg.
 
 N > 1 (``torchrun``): the GEMM is sharded along N with no data-path collective (every rank
 owns its own 8192-column block of B and of C; A and scale_a are replicated), weak scaling;
@@ -195,6 +196,47 @@ def run_reference_arm(args, rank):
     print(json.dumps(line))
 
 
+class HostPipeline:
+    """End-to-end loop with host operands: every step copies its inputs from pinned host memory,
+    runs ``compute(device_inputs)`` through the public API and copies the result back.  The
+    three legs of consecutive steps overlap (copy-in stream, compute stream, copy-out stream,
+    two sets of device buffers), as a serving loop would run them: PCIe is full duplex, so the
+    step rate is set by the slowest leg, not by the sum."""
+
+    def __init__(self, host_inputs, host_out, compute, device):
+        self.host_inputs, self.host_out, self.compute_fn, self.device = host_inputs, host_out, compute, device
+        self.copy_in, self.copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        self.sets = [dict(inputs=[torch.empty_like(t, device=device) for t in host_inputs],
+                          loaded=torch.cuda.Event(), computed=torch.cuda.Event(),
+                          drained=torch.cuda.Event(), result=None) for _ in range(2)]
+
+    def step(self, index):
+        buffers = self.sets[index % 2]
+        compute = torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(self.copy_in):
+            self.copy_in.wait_event(buffers["computed"])   # the set's previous step has read it
+            for target, source in zip(buffers["inputs"], self.host_inputs):
+                target.copy_(source, non_blocking=True)
+            buffers["loaded"].record(self.copy_in)
+        compute.wait_event(buffers["loaded"])
+        compute.wait_event(buffers["drained"])             # the set's previous result has left
+        result = self.compute_fn(buffers["inputs"])
+        result.record_stream(self.copy_out)
+        buffers["result"] = result
+        buffers["computed"].record(compute)
+        with torch.cuda.stream(self.copy_out):
+            self.copy_out.wait_event(buffers["computed"])
+            self.host_out.copy_(result, non_blocking=True)
+            buffers["drained"].record(self.copy_out)
+
+    def run(self, steps, first=0):
+        for index in range(first, first + steps):
+            self.step(index)
+        compute = torch.cuda.current_stream(self.device)
+        compute.wait_stream(self.copy_out)
+        compute.wait_stream(self.copy_in)
+
+
 def run_moe(args, rank, world, device, barrier):
     """Times the MoE FFN: single GPU at world == 1, expert parallel (NCCL all-to-all) beyond.
     Returns the rank-0 report (None on other ranks)."""
@@ -228,17 +270,16 @@ def run_moe(args, rank, world, device, barrier):
     host = {n: case[n].cpu().pin_memory() for n in token_names}
     host_out = torch.empty(case["hidden_states"].shape, dtype=torch.bfloat16).pin_memory()
 
-    def e2e_step():
+    def from_device_inputs(inputs):
         tensors = dict(case)
-        for n in token_names:
-            tensors[n] = host[n].to(device, non_blocking=True)
-        host_out.copy_(step(tensors), non_blocking=True)
+        tensors.update(zip(token_names, inputs))
+        return step(tensors)
 
-    e2e_step()
+    pipeline = HostPipeline([host[n] for n in token_names], host_out, from_device_inputs, device)
+    pipeline.run(2)
     barrier()
     start.record()
-    for _ in range(steps):
-        e2e_step()
+    pipeline.run(steps, first=2)
     stop.record()
     barrier()
     e2e_elapsed = torch.tensor([start.elapsed_time(stop) / steps], device=device)
@@ -342,18 +383,15 @@ def main():
         h2d = sum(t.numel() * t.element_size() for t in host)
         d2h = host_out.numel() * host_out.element_size()
 
-        def e2e_step():
-            da, dw, dsa, dsb = (t.to(device, non_blocking=True) for t in host)
-            result = gemm.int8_gemm(da, dw.t(), dsa, dsb, group_size=g, output_dtype=torch.bfloat16)
-            host_out.copy_(result, non_blocking=True)
-
-        e2e_steps = max(2, min(args.steps, 5))
-        for _ in range(2):
-            e2e_step()
+        pipeline = HostPipeline(
+            host, host_out,
+            lambda t: gemm.int8_gemm(t[0], t[1].t(), t[2], t[3], group_size=g,
+                                     output_dtype=torch.bfloat16), device)
+        e2e_steps = max(4, min(args.steps, 10))
+        pipeline.run(2)
         barrier()
         start.record()
-        for _ in range(e2e_steps):
-            e2e_step()
+        pipeline.run(e2e_steps, first=2)
         stop.record()
         barrier()
         e2e_ms = start.elapsed_time(stop)
