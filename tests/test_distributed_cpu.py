@@ -81,6 +81,8 @@ def worker(rank, world, port, scenario, results):
         dist.init_process_group("gloo", rank=rank, world_size=world)
         from grain_gemm_b200 import distributed
         case = full_case()
+        if scenario == "one_sided":
+            case["topk_ids"] = case["topk_ids"] % 3   # every expert used lives on rank 0
         if scenario == "invalid_id":
             case["token_mask"][:] = True
             case["topk_ids"][1, 0] = 6           # token 1 belongs to rank 0 only
@@ -114,6 +116,17 @@ def test_expert_parallel_equals_single_process_bit_for_bit():
     actual = torch.cat([results[0][1], results[1][1]])
     assert torch.equal(actual, expected)
     assert actual[~case["token_mask"]].abs().sum() == 0
+
+
+def test_rank_without_incoming_tokens():
+    """All assignments go to rank 0's experts: rank 1 receives nothing and still takes part in
+    every collective; repeated experts within a token travel as one row."""
+    results = run_scenario("one_sided")
+    assert all(results[r][0] == "ok" for r in range(2)), results
+    case = full_case()
+    case["topk_ids"] = case["topk_ids"] % 3
+    expected = oracle.moe_ffn(**case).float()
+    assert torch.equal(torch.cat([results[0][1], results[1][1]]), expected)
 
 
 def test_invalid_id_on_one_rank_raises_everywhere():
