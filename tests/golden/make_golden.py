@@ -1,9 +1,9 @@
 """Generate the golden fixtures in this folder from the reference project itself.
 
-Run once, in a container that has the reference checked out (default location
-``/root/reference``; override with ``GRAIN_REFERENCE_DIR``):
+Run once, in a container that has the reference checked out; its location comes from the
+environment:
 
-    python tests/golden/make_golden.py
+    GRAIN_REFERENCE_DIR=<reference checkout> python tests/golden/make_golden.py
 
 Two sources are used, both the reference's own code, unmodified:
 
@@ -23,7 +23,9 @@ import sys
 from pathlib import Path
 
 os.environ["TRITON_INTERPRET"] = "1"
-REFERENCE = Path(os.environ.get("GRAIN_REFERENCE_DIR", "/root/reference"))
+if "GRAIN_REFERENCE_DIR" not in os.environ:
+    raise SystemExit("set GRAIN_REFERENCE_DIR to the reference checkout")
+REFERENCE = Path(os.environ["GRAIN_REFERENCE_DIR"])
 sys.path.insert(0, str(REFERENCE / "src"))
 sys.path.insert(0, str(REFERENCE / "tests"))
 sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
