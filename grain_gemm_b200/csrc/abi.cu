@@ -712,6 +712,31 @@ int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_
   return gg::launch_simt_dtype<true>(p, tile_capacity, out_dtype, stream);
 }
 
+int gg_moe_topk(const void* logits, int in_dtype, int tokens, int experts, int top_k, void* weights,
+                void* ids, int ids_are_i64, void* stream_ptr) {
+  if (tokens < 0 || experts <= 0 || experts > 1024 || top_k <= 0 || top_k > experts ||
+      (in_dtype != GG_OUT_FP32 && in_dtype != GG_OUT_BF16 && in_dtype != GG_OUT_FP16)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (tokens == 0) return 0;
+  if (!logits || !weights || !ids) return static_cast<int>(cudaErrorInvalidValue);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const int grid = (tokens + 7) / 8;
+  float* w = static_cast<float*>(weights);
+  if (in_dtype == GG_OUT_FP32) {
+    gg::router_topk_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(logits), tokens,
+                                                             experts, top_k, w, ids, ids_are_i64);
+  } else if (in_dtype == GG_OUT_BF16) {
+    gg::router_topk_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(logits), tokens, experts, top_k, w, ids, ids_are_i64);
+  } else {
+    gg::router_topk_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(logits),
+                                                              tokens, experts, top_k, w, ids,
+                                                              ids_are_i64);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
 int gg_quantize_rows(const void* x, int in_dtype, long long rows, int width, int group_size,
                      void* q, void* s, void* stream_ptr) {
   const bool group_ok = group_size == 32 || group_size == 64 || group_size == 128 || group_size == 256;

@@ -283,6 +283,80 @@ __device__ __forceinline__ int quantize_value_by_fma(float h, float scale, float
   return static_cast<int>(fminf(fmaxf(rounded, -127.0f), 127.0f));
 }
 
+// Router front-end: per token, the top_k largest of E logits (ties to the lower expert id,
+// ids in descending order of logit, like torch.topk on distinct values) and their routing
+// weights softmax(logits)[id] renormalised over the selection, i.e.
+//   w_i = exp(l_i - l_max) / sum_{j selected} exp(l_j - l_max),
+// the logits -> softmax -> top-k -> renormalise step in front of routing (the reference leaves
+// it to the caller: benchmarks/bench_moe_ffn.py:283-285, docs/moe_ffn.md:5-7).  One warp per
+// token; expert e lives in lane e % 32, slot e / 32 (E <= 1024).  Logits must be finite.
+template <typename InT>
+__global__ void __launch_bounds__(256)
+router_topk_kernel(const InT* __restrict__ logits, int tokens, int experts, int top_k,
+                   float* __restrict__ weights, void* __restrict__ ids, int ids_are_i64) {
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (token >= tokens) return;
+  const InT* row = logits + static_cast<long long>(token) * experts;
+  constexpr float kLowest = -3.402823466e+38f;
+  float value[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int e = lane + 32 * i;
+    value[i] = e < experts ? static_cast<float>(row[e]) : kLowest;
+  }
+  float first = 0.0f, total = 0.0f, mine = 0.0f;   // lane r keeps the r-th weight
+  int mine_id = 0;
+  for (int r = 0; r < top_k; ++r) {
+    float best = kLowest;
+    int best_id = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (value[i] > best) {   // slots ascend in expert id: the first maximum wins a tie
+        best = value[i];
+        best_id = lane + 32 * i;
+      }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_id = __shfl_xor_sync(0xffffffffu, best_id, offset);
+      if (other > best || (other == best && other_id < best_id)) {
+        best = other;
+        best_id = other_id;
+      }
+    }
+    if (r == 0) first = best;
+    const float weight = expf(best - first);
+    total += weight;
+    if (lane == (r & 31)) {
+      mine = weight;
+      mine_id = best_id;
+    }
+    if ((best_id & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i == (best_id >> 5)) value[i] = kLowest;
+      }
+    }
+    if ((r & 31) == 31 || r == top_k - 1) {
+      // Flush up to 32 selections; weights are divided by the final total below.
+      const int base = r & ~31;
+      if (lane <= (r & 31)) {
+        const long long slot = static_cast<long long>(token) * top_k + base + lane;
+        weights[slot] = mine;
+        if (ids_are_i64) reinterpret_cast<long long*>(ids)[slot] = mine_id;
+        else reinterpret_cast<int*>(ids)[slot] = mine_id;
+      }
+    }
+  }
+  __syncwarp();
+  for (int r = lane; r < top_k; r += 32) {
+    const long long slot = static_cast<long long>(token) * top_k + r;
+    weights[slot] = __fdiv_rn(weights[slot], total);
+  }
+}
+
 // Entry quantiser: symmetric per-row, per-K-group INT8 quantisation of floating rows,
 // restating quantize_rows (src/grain_gemm/kernels/moe.py:321-356):
 //   scale = div_rn(max(amax, 1e-12), 127);  q = clamp(nearbyint(div_rn(v, scale)), +-127).

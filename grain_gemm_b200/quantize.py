@@ -4,6 +4,8 @@ preparation, with the reference's names and conventions.
 * ``quantize_rows`` mirrors ``quantize_rows`` of ``src/grain_gemm/kernels/moe.py:344-356`` of
   the reference (symmetric INT8, one FP32 scale per row and K group) and runs the CUDA kernel
   behind ``gg_quantize_rows``.
+* ``route_topk`` is the router front-end (logits -> softmax -> top-k -> renormalise) that the
+  reference leaves to its callers (``benchmarks/bench_moe_ffn.py:283-285``).
 * ``prepare_weight`` and ``interleave_gate_up`` restate the preparation recipes of the
   reference's ``docs/moe_ffn.md:119-133`` and ``docs/moe_interleaved.md:32-40``; they run once,
   outside the forward pass, as plain tensor operations.
@@ -52,6 +54,37 @@ def quantize_rows(x, group_size=256, *, rows_per_program=4):
                 _loader.pointer(quantized), _loader.pointer(scales),
                 _loader.stream_pointer(x.device)), "gg_quantize_rows")
     return quantized, scales
+
+
+def route_topk(logits, top_k, *, ids_dtype=torch.int64):
+    """Router front-end: the ``top_k`` experts of every token and their routing weights.
+
+    ``logits`` is ``[T, E]`` (FP32, BF16 or FP16, contiguous, finite, ``E <= 1024``).  Returns
+    ``(topk_weights [T, top_k] FP32, topk_ids [T, top_k])`` ready for ``moe_ffn``: ids in
+    descending order of logit (ties to the lower id) and ``softmax(logits)`` of the selected
+    experts renormalised to sum to one.
+    """
+    if not isinstance(logits, torch.Tensor) or logits.dim() != 2:
+        raise ValueError("logits must be a [T, E] tensor")
+    if logits.dtype not in _loader.OUT_DTYPE:
+        raise ValueError("logits must be torch.float32, torch.bfloat16 or torch.float16")
+    tokens, experts = logits.shape
+    if not 0 < top_k <= experts or experts > 1024:
+        raise ValueError("need 0 < top_k <= E <= 1024")
+    if ids_dtype not in (torch.int32, torch.int64):
+        raise ValueError("ids_dtype must be torch.int32 or torch.int64")
+    if logits.device.type != "cuda" or not logits.is_contiguous():
+        raise ValueError("logits must be a contiguous CUDA tensor")
+    weights = torch.empty((tokens, top_k), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((tokens, top_k), dtype=ids_dtype, device=logits.device)
+    if tokens:
+        lib = _loader.library()
+        with torch.cuda.device(logits.device):
+            _loader.check(lib.gg_moe_topk(
+                _loader.pointer(logits), _loader.OUT_DTYPE[logits.dtype], tokens, experts, top_k,
+                _loader.pointer(weights), _loader.pointer(ids), int(ids_dtype == torch.int64),
+                _loader.stream_pointer(logits.device)), "gg_moe_topk")
+    return weights, ids
 
 
 def prepare_weight(linear_weight, group_size=256):

@@ -154,6 +154,17 @@ int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, 
                  void* tile_row, void* stream);
 
 /*
+ * Router front-end (the step before gg_moe_route): per token the top_k largest of `experts`
+ * logits (<= 1024; ties to the lower id; ids in descending order of logit) and their weights
+ * softmax(logits)[id] renormalised over the selection.  logits[tokens, experts] contiguous of
+ * dtype in_dtype (GG_OUT_FP32/BF16/FP16 name the element type), finite; weights[tokens, top_k]
+ * fp32; ids[tokens, top_k] int32 or int64.  The reference leaves this step to the caller
+ * (benchmarks/bench_moe_ffn.py:283-285, docs/moe_ffn.md:5-7).
+ */
+int gg_moe_topk(const void* logits, int in_dtype, int tokens, int experts, int top_k, void* weights,
+                void* ids, int ids_are_i64, void* stream);
+
+/*
  * Entry quantiser (the step before both paths): x[rows, width] of dtype in_dtype (GG_OUT_FP32,
  * GG_OUT_BF16 or GG_OUT_FP16 name the element type), contiguous, width a multiple of 256,
  * 16-byte aligned; writes q[rows, width] int8 and s[rows, width/group_size] fp32 with

@@ -126,6 +126,23 @@ def swiglu_quantize(gate_up, valid_rows=None, gate_up_layout="split"):
     return q, s
 
 
+def router_topk(logits, top_k):
+    """Router front-end: logits -> softmax -> top-k -> renormalise, as the reference's callers do
+    it before ``moe_ffn`` (``benchmarks/bench_moe_ffn.py:283-285``, ``docs/moe_ffn.md:5-7``).
+
+    Ids in descending order of logit, ties to the lower id; weights
+    ``exp(l_i - l_max) / sum_selected exp(l_j - l_max)`` with the sum taken in selection order.
+    """
+    values = logits.float()
+    order = torch.argsort(-values, dim=-1, stable=True)[:, :top_k]
+    selected = values.gather(1, order)
+    weights = torch.exp(selected - selected[:, :1])
+    total = torch.zeros_like(weights[:, 0])
+    for r in range(top_k):
+        total = total + weights[:, r]
+    return weights / total[:, None], order
+
+
 def quantize_rows(x, group_size=256):
     """Entry quantiser; restates ``quantize_rows`` (``src/grain_gemm/kernels/moe.py:321-356``).
 

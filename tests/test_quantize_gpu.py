@@ -88,3 +88,36 @@ def test_prepare_weight_and_interleave(quantize):
     assert qi.stride() == q.stride()
     assert torch.equal(qi[..., 0::2], q[..., :inter]) and torch.equal(qi[..., 1::2], q[..., inter:])
     assert torch.equal(si[..., 0::2], s[..., :inter]) and torch.equal(si[..., 1::2], s[..., inter:])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("experts,top_k", [(8, 2), (128, 8), (256, 8), (1000, 6), (40, 40)])
+def test_router_front_end(quantize, dtype, experts, top_k):
+    gen = torch.Generator().manual_seed(experts + top_k)
+    logits = (torch.randn((333, experts), generator=gen) * 2).to(dtype)
+    logits[5, :] = 0.25                       # all tied: the lowest ids win, in order
+    weights, ids = quantize.route_topk(logits.cuda(), top_k)
+    expected_weights, expected_ids = oracle.router_topk(logits, top_k)
+    assert torch.equal(ids.cpu(), expected_ids)
+    assert ids[5].tolist() == list(range(top_k))
+    torch.testing.assert_close(weights.cpu(), expected_weights, rtol=2e-6, atol=1e-9)
+    torch.testing.assert_close(weights.sum(-1).cpu(), torch.ones(333), rtol=1e-6, atol=0)
+    reference = torch.softmax(logits.float(), -1).gather(1, expected_ids)
+    torch.testing.assert_close(weights.cpu(), reference / reference.sum(-1, keepdim=True),
+                               rtol=1e-5, atol=1e-9)
+    small, small_ids = quantize.route_topk(logits.cuda(), top_k, ids_dtype=torch.int32)
+    assert small_ids.dtype == torch.int32 and torch.equal(small_ids.long().cpu(), expected_ids)
+
+
+def test_router_output_feeds_moe_ffn(quantize):
+    from grain_gemm_b200 import moe_ffn
+    gen = torch.Generator().manual_seed(21)
+    tokens, hidden, inter, experts, top_k = 50, 512, 256, 6, 2
+    x, sx = quantize.quantize_rows(torch.randn((tokens, hidden), generator=gen).cuda())
+    w1, s1 = quantize.prepare_weight((torch.randn((experts, 2 * inter, hidden), generator=gen) / hidden ** 0.5).cuda())
+    w2, s2 = quantize.prepare_weight((torch.randn((experts, hidden, inter), generator=gen) / inter ** 0.5).cuda())
+    weights, ids = quantize.route_topk(torch.randn((tokens, experts), generator=gen).cuda(), top_k)
+    out = moe_ffn(x, w1, w2, weights, ids, scale_x=sx, scale_gate_up=s1, scale_down=s2)
+    expected = oracle.moe_ffn(x.cpu(), w1.cpu(), w2.cpu(), weights.cpu(), ids.cpu(), scale_x=sx.cpu(),
+                              scale_gate_up=s1.cpu(), scale_down=s2.cpu())
+    torch.testing.assert_close(out.float().cpu(), expected.float(), rtol=1e-3, atol=1e-2)
