@@ -778,12 +778,19 @@ int gg_moe_combine(const void* expert_out, const void* weights, const void* inve
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   const size_t smem = static_cast<size_t>(top_k) * 8;
   if (smem > 48 * 1024) return static_cast<int>(cudaErrorInvalidValue);
+  // Threads per token: the 16-byte chunks of a row spread evenly over whole passes
+  // (H = 7168: 896 chunks, 4 passes of 224 threads instead of 3.5 of 256).
+  const int chunks = (hidden + 7) / 8;
+  const int passes = (chunks + 255) / 256;
+  int threads = ((chunks + passes - 1) / passes + 31) / 32 * 32;
+  if (threads > 256) threads = 256;
+  if (threads < 32) threads = 32;
   if (out_dtype == GG_OUT_BF16) {
-    gg::combine_kernel<__nv_bfloat16><<<tokens, 256, smem, stream>>>(
+    gg::combine_kernel<__nv_bfloat16><<<tokens, threads, smem, stream>>>(
         static_cast<const __nv_bfloat16*>(expert_out), static_cast<const float*>(weights),
         static_cast<const int*>(inverse), static_cast<__nv_bfloat16*>(out), top_k, hidden);
   } else {
-    gg::combine_kernel<__half><<<tokens, 256, smem, stream>>>(
+    gg::combine_kernel<__half><<<tokens, threads, smem, stream>>>(
         static_cast<const __half*>(expert_out), static_cast<const float*>(weights),
         static_cast<const int*>(inverse), static_cast<__half*>(out), top_k, hidden);
   }

@@ -465,16 +465,28 @@ combine_kernel(const T* __restrict__ expert_out, const float* __restrict__ weigh
   if (vector_ok) {
     for (int col = threadIdx.x * 8; col < hidden; col += blockDim.x * 8) {
       float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int r = 0; r < top_k; ++r) {
-        const int slot = slot_smem[r];
-        if (slot < 0) continue;
-        const float w = weight_smem[r];
-        const uint4 packed =
-            *reinterpret_cast<const uint4*>(expert_out + static_cast<long long>(slot) * hidden + col);
-        const T* values = reinterpret_cast<const T*>(&packed);
+      // Four rows are fetched before any is added, so that a thread keeps four 16-byte loads
+      // in flight; the additions stay in slot order.
+      for (int r0 = 0; r0 < top_k; r0 += 4) {
+        uint4 packed[4];
+        int slot[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          total[i] = __fadd_rn(total[i], __fmul_rn(static_cast<float>(values[i]), w));
+        for (int j = 0; j < 4; ++j) {
+          slot[j] = r0 + j < top_k ? slot_smem[r0 + j] : -1;
+          if (slot[j] >= 0) {
+            packed[j] = *reinterpret_cast<const uint4*>(
+                expert_out + static_cast<long long>(slot[j]) * hidden + col);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (slot[j] < 0) continue;
+          const float w = weight_smem[r0 + j];
+          const T* values = reinterpret_cast<const T*>(&packed[j]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            total[i] = __fadd_rn(total[i], __fmul_rn(static_cast<float>(values[i]), w));
+        }
       }
       uint4 packed_out;
       T* outputs = reinterpret_cast<T*>(&packed_out);
