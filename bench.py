@@ -242,7 +242,8 @@ def run_moe(args, rank, world, device, barrier):
     Returns the rank-0 report (None on other ranks)."""
     import torch.distributed as dist
 
-    from grain_gemm_b200 import bench_moe, distributed, moe
+    import bench_moe
+    from grain_gemm_b200 import distributed, moe
 
     name = args.moe_config
     config = bench_moe.CONFIGS[name]

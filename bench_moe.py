@@ -1,6 +1,6 @@
-"""Synthetic MoE FFN workloads and their timing (used by ``bench.py``).
+"""Synthetic MoE FFN workloads and their timing (used by ``bench.py`` and the GPU tests).
 
-Configurations follow BASELINE.json: ``decode_small`` (T=512, H=2048, I=768, E=128, top-8,
+Configurations: ``decode_small`` (T=512, H=2048, I=768, E=128, top-8,
 split), ``interleaved_decode`` / ``interleaved_prefill`` (H=4096, I=14336, E=8, top-2, T=16 /
 4096, one expert biased, interleaved gate/up) and ``large`` (T=16384, H=7168, I=2048, E=256,
 top-8), the expert-parallel case, and ``large_rank_share`` (T=2048, E=32 of the same shape: the
@@ -121,7 +121,7 @@ def algorithmic_bytes(name, active_experts=None):
 
 def time_stages(case, steps, warmup):
     """Per-stage and total device time (ms per call) of the single-GPU FFN."""
-    from . import moe
+    from grain_gemm_b200 import moe
 
     device = case["hidden_states"].device
     experts = case["w_gate_up"].shape[0]

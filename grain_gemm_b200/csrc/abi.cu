@@ -129,10 +129,10 @@ static int select_variant(const GemmArgs& g) {
 
 template <typename OutT, bool kRagged>
 static int launch_simt(const GemmSimtParams& p, int row_tiles, cudaStream_t stream) {
-  const dim3 grid((p.n + kSimtTile - 1) / kSimtTile, row_tiles);
-  if (grid.x == 0 || grid.y == 0) return 0;
-  if (grid.y > 65535) return static_cast<int>(cudaErrorInvalidValue);
-  gemm_simt_kernel<OutT, kRagged><<<grid, 256, 0, stream>>>(p);
+  const long long blocks = static_cast<long long>((p.n + kSimtTile - 1) / kSimtTile) * row_tiles;
+  if (blocks <= 0) return 0;
+  if (blocks > 0x7fffffffLL) return static_cast<int>(cudaErrorInvalidValue);
+  gemm_simt_kernel<OutT, kRagged><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -322,6 +322,22 @@ static int run_gemm(const GemmArgs& g, int variant, cudaStream_t stream, void* w
   return launch_gemm_tc(g, variant, stream);
 }
 
+// One warp waits, with the kernels' own bounded wait, on a barrier that nothing ever
+// completes: the wait gives up after `limit_ns`, records (kSiteSelfTest << 8) | 1 in the device
+// status word and the kernel returns normally.  *result = 1 if the wait reported success.
+__global__ void wait_timeout_probe_kernel(unsigned long long limit_ns, int* result) {
+  __shared__ uint64_t barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&barrier, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const bool completed = mbar_wait_warp(&barrier, 0u, kSiteSelfTest, &abort_flag, limit_ns);
+  if (threadIdx.x == 0) *result = completed ? 1 : 0;
+}
+
 }  // namespace gg
 
 // ------------------------------------------------------------------ extern "C"
@@ -437,6 +453,9 @@ int gg_moe_route(const void* ids, int ids_are_i64, const void* mask, int tokens,
   const long long slots = static_cast<long long>(tokens) * top_k;
   const size_t smem = static_cast<size_t>(experts + 2) * sizeof(int);
   if (smem > 200 * 1024) return static_cast<int>(cudaErrorInvalidValue);
+  if (slots > 0 && (!ids || !effective_ids || !order || !inverse)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
   cudaError_t error;
   if (slots <= gg::kRouteChunk) {
     if (smem > 48 * 1024) {
@@ -447,7 +466,6 @@ int gg_moe_route(const void* ids, int ids_are_i64, const void* mask, int tokens,
     gg::route_single_kernel<<<1, gg::kRouteChunk, smem, stream>>>(p);
     return static_cast<int>(cudaGetLastError());
   }
-  if (!ids || !effective_ids || !order || !inverse) return static_cast<int>(cudaErrorInvalidValue);
   if (workspace_bytes < gg_moe_route_workspace_bytes(tokens, top_k, experts) || !workspace) {
     return static_cast<int>(cudaErrorInvalidValue);
   }
@@ -775,6 +793,10 @@ int gg_moe_combine(const void* expert_out, const void* weights, const void* inve
     return static_cast<int>(cudaErrorInvalidValue);
   }
   if (tokens == 0) return 0;
+  if (!expert_out) return static_cast<int>(cudaErrorInvalidValue);
+  // Rows move as 16-byte vectors when H is a multiple of 8 and both bases are aligned;
+  // anything else takes the element-wise loop.
+  const int vector_ok = hidden % 8 == 0 && gg::aligned16(expert_out) && gg::aligned16(out);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   const size_t smem = static_cast<size_t>(top_k) * 8;
   if (smem > 48 * 1024) return static_cast<int>(cudaErrorInvalidValue);
@@ -788,12 +810,21 @@ int gg_moe_combine(const void* expert_out, const void* weights, const void* inve
   if (out_dtype == GG_OUT_BF16) {
     gg::combine_kernel<__nv_bfloat16><<<tokens, threads, smem, stream>>>(
         static_cast<const __nv_bfloat16*>(expert_out), static_cast<const float*>(weights),
-        static_cast<const int*>(inverse), static_cast<__nv_bfloat16*>(out), top_k, hidden);
+        static_cast<const int*>(inverse), static_cast<__nv_bfloat16*>(out), top_k, hidden, vector_ok);
   } else {
     gg::combine_kernel<__half><<<tokens, threads, smem, stream>>>(
         static_cast<const __half*>(expert_out), static_cast<const float*>(weights),
-        static_cast<const int*>(inverse), static_cast<__half*>(out), top_k, hidden);
+        static_cast<const int*>(inverse), static_cast<__half*>(out), top_k, hidden, vector_ok);
   }
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gg_selftest_wait_timeout(long long limit_ns, void* result, void* stream_ptr) {
+  if (limit_ns <= 0 || limit_ns > 100000000ll || !result) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  gg::wait_timeout_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      static_cast<unsigned long long>(limit_ns), static_cast<int*>(result));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -816,17 +847,5 @@ int gg_device_status(int* status, void* stream_ptr) {
   }
   return static_cast<int>(error);
 }
-
-#ifdef GG_TRACE
-// Debug builds only: copies the CTA-0 timeline to host memory (synchronises the device).
-int gg_debug_trace(long long* out, int entries) {
-  cudaError_t error = cudaDeviceSynchronize();
-  if (error != cudaSuccess) return static_cast<int>(error);
-  error = cudaMemcpyFromSymbol(out, gg::g_trace, sizeof(long long) * entries);
-  if (error != cudaSuccess) return static_cast<int>(error);
-  static long long zeros[3 * 2048];
-  return static_cast<int>(cudaMemcpyToSymbol(gg::g_trace, zeros, sizeof(zeros)));
-}
-#endif
 
 }  // extern "C"

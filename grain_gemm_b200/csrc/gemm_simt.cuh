@@ -62,19 +62,22 @@ gemm_simt_kernel(const GemmSimtParams p) {
 
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
-  const int n0 = blockIdx.x * kSimtTile;
+  // One-dimensional grid (row tiles can exceed the 65535 limit of grid.y): column tile fastest.
+  const int tiles_n = (p.n + kSimtTile - 1) / kSimtTile;
+  const int tile_m = blockIdx.x / tiles_n;
+  const int n0 = (blockIdx.x - tile_m * tiles_n) * kSimtTile;
   int row0, row_limit;
   const int8_t* b = p.b;
   const float* sb = p.scale_b;
   if constexpr (kRagged) {
-    const int expert = p.tile_expert[blockIdx.y];
+    const int expert = p.tile_expert[tile_m];
     if (expert < 0) return;
-    row0 = p.tile_row[blockIdx.y];
+    row0 = p.tile_row[tile_m];
     row_limit = p.expert_offsets[expert + 1];
     b += static_cast<long long>(expert) * p.b_expert_stride;
     sb += static_cast<long long>(expert) * p.sb_expert_stride;
   } else {
-    row0 = blockIdx.y * kSimtTile;
+    row0 = tile_m * kSimtTile;
     row_limit = p.m;
   }
   if (tid < kSimtTile) {

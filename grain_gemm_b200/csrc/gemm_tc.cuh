@@ -35,6 +35,25 @@
 
 namespace gg {
 
+// Build switches (both on in the shipped library; the off positions are kept for measurements).
+//  GG_TMEM_BIAS      accumulators preset to kAccumulatorBias, float(dot) by one FP32 subtraction
+//  GG_SCALE_PERMUTE  scale ring stored in the order the promotion threads read it (16-byte loads)
+#ifndef GG_TMEM_BIAS
+#define GG_TMEM_BIAS 1
+#endif
+#ifndef GG_SCALE_PERMUTE
+#define GG_SCALE_PERMUTE 1
+#endif
+// Register split between the eight promotion warps and the four auxiliary warps (setmaxnreg).
+#ifndef GG_PROMO_REGS
+#define GG_PROMO_REGS 216
+#endif
+#ifndef GG_AUX_REGS
+#define GG_AUX_REGS 64
+#endif
+constexpr bool kTmemBias = GG_TMEM_BIAS != 0;
+constexpr bool kScalePermute = GG_SCALE_PERMUTE != 0;
+
 struct GemmTcParams {
   const float* scale_a;
   const float* scale_b;
@@ -91,8 +110,8 @@ struct GemmTcShape {
   static constexpr int kThreads = (kPromoWarps + 4) * 32;   // + producer, MMA, two spares
   static constexpr int kColumnsPerThread = BN / (kPromoWarps / 4);
   static constexpr int kDrainWidth = kPromoWarps == 16 ? 16 : 32;  // columns per tcgen05.ld
-  static constexpr int kPromoRegisters = kPromoWarps == 16 ? 104 : 216;
-  static constexpr int kAuxRegisters = kPromoWarps == 16 ? 48 : 64;
+  static constexpr int kPromoRegisters = kPromoWarps == 16 ? 104 : GG_PROMO_REGS;
+  static constexpr int kAuxRegisters = kPromoWarps == 16 ? 48 : GG_AUX_REGS;
   // setmaxnreg can only hand the promotion warps registers that the four other warps of the
   // same CTA released: (promo - launch) * promo threads <= (launch - aux) * 128, where launch
   // is the per-thread count the kernel starts with under its launch bound.
@@ -139,20 +158,71 @@ __device__ __forceinline__ TileWork decode_tile(const GemmTcParams& p, int tile)
   return w;
 }
 
+// Position of accumulator column `c` (0..31 within its 32-column block) in the scale ring:
+// the thread with quad index q = lane % 4 reads the eight scales of its columns
+// 8i + 2q, 8i + 2q + 1 (i = 0..3) as two 16-byte vectors at q * 8.
+__device__ __forceinline__ int ring_column_position(int c) {
+  return kScalePermute ? ((c >> 1) & 3) * 8 + (c >> 3) * 2 + (c & 1) : c;
+}
+// Position of row `r` (0..31 within its warp's 32 rows): the thread with row index
+// lane / 4 = r % 8 reads its four rows r % 8 + 8j as one 16-byte vector.
+__device__ __forceinline__ int ring_row_position(int r) {
+  return kScalePermute ? (r & 7) * 4 + (r >> 3) : r;
+}
+
+// The eight column scales (four pairs) of this thread for one 32-column block.
+__device__ __forceinline__ void load_column_scales(const float* block_base, int quad,
+                                                   float2 (&sb)[4]) {
+  if constexpr (kScalePermute) {
+    const float4 lo = *reinterpret_cast<const float4*>(block_base + quad * 8);
+    const float4 hi = *reinterpret_cast<const float4*>(block_base + quad * 8 + 4);
+    sb[0] = make_float2(lo.x, lo.y);
+    sb[1] = make_float2(lo.z, lo.w);
+    sb[2] = make_float2(hi.x, hi.y);
+    sb[3] = make_float2(hi.z, hi.w);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      sb[i] = *reinterpret_cast<const float2*>(block_base + 8 * i + 2 * quad);
+  }
+}
+// The four row scales of this thread (rows fragment_row + 8j of the warp's 32 rows).
+__device__ __forceinline__ void load_row_scales(const float* warp_rows_base, int fragment_row,
+                                                float (&sa)[4]) {
+  if constexpr (kScalePermute) {
+    const float4 v = *reinterpret_cast<const float4*>(warp_rows_base + fragment_row * 4);
+    sa[0] = v.x; sa[1] = v.y; sa[2] = v.z; sa[3] = v.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sa[j] = warp_rows_base[fragment_row + 8 * j];
+  }
+}
+
 // Promotion of one 16-row x 32-column fragment (tmem_ld_16x256b_x4 layout): this thread holds
 // rows r and r+8 and column pairs 8i+2q, 8i+2q+1.  `sb` are its four column-scale pairs, read
-// once per 32-column block and used for both 16-row halves.
+// once per 32-column block and used for both 16-row halves.  kBiased: the words are
+// kAccumulatorBias + dot (see ptx.cuh) and float(dot) is an exact packed subtraction.
+template <bool kBiased>
 __device__ __forceinline__ void promote_fragment(const uint32_t (&partial)[16], float sa_low,
                                                  float sa_high, const float2 (&sb)[4],
                                                  float2* acc_low, float2* acc_high) {
   const float2 sa_low2 = make_float2(sa_low, sa_low);
   const float2 sa_high2 = make_float2(sa_high, sa_high);
+  const float2 minus_bias = make_float2(-kAccumulatorBiasValue, -kAccumulatorBiasValue);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 low = make_float2(__int2float_rn(static_cast<int>(partial[4 * i + 0])),
-                                   __int2float_rn(static_cast<int>(partial[4 * i + 1])));
-    const float2 high = make_float2(__int2float_rn(static_cast<int>(partial[4 * i + 2])),
-                                    __int2float_rn(static_cast<int>(partial[4 * i + 3])));
+    float2 low, high;
+    if constexpr (kBiased) {
+      low = __fadd2_rn(make_float2(__uint_as_float(partial[4 * i + 0]),
+                                   __uint_as_float(partial[4 * i + 1])), minus_bias);
+      high = __fadd2_rn(make_float2(__uint_as_float(partial[4 * i + 2]),
+                                    __uint_as_float(partial[4 * i + 3])), minus_bias);
+    } else {
+      low = make_float2(__int2float_rn(static_cast<int>(partial[4 * i + 0])),
+                        __int2float_rn(static_cast<int>(partial[4 * i + 1])));
+      high = make_float2(__int2float_rn(static_cast<int>(partial[4 * i + 2])),
+                         __int2float_rn(static_cast<int>(partial[4 * i + 3])));
+    }
     acc_low[i] = __ffma2_rn(low, __fmul2_rn(sa_low2, sb[i]), acc_low[i]);
     acc_high[i] = __ffma2_rn(high, __fmul2_rn(sa_high2, sb[i]), acc_high[i]);
   }
@@ -247,6 +317,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if constexpr (kCtaGroup == 2) cluster_sync_all();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  constexpr bool kBias = kTmemBias && !kDump;
+
+  if constexpr (kBias) {
+    // Every accumulator word starts at the bias: each promotion warp presets the lanes and
+    // columns it will later drain, in both buffers, before the first MMA may be issued.
+    if (warp < kPromoWarps) {
+      uint32_t bias[16];
+      make_bias_block(bias);
+      const uint32_t lanes = static_cast<uint32_t>((warp & 3) * 32) << 16;
+#pragma unroll
+      for (int buffer = 0; buffer < 2; ++buffer) {
+#pragma unroll
+        for (int block = 0; block < kNC / 32; ++block) {
+          const uint32_t taddr = tmem_base + lanes + buffer * BN + (warp >> 2) * kNC + block * 32;
+          tmem_st_16x256b_x4(taddr, bias);
+          tmem_st_16x256b_x4(taddr + (16u << 16), bias);
+        }
+      }
+      tmem_st_wait();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if constexpr (kCtaGroup == 2) cluster_sync_all();
+    tcgen05_fence_after();
+  }
 
   // The last four warps (producer, MMA issuer, two spares) give registers to the promotion warps.
   if (warp >= kPromoWarps) {
@@ -257,7 +352,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const bool leader = elect_one();
     uint32_t stage = 0, phase = 0;
     bool ok = true;
-    [[maybe_unused]] int trace_cursor = 0;
     for (int tile = worker; tile < total_tiles && ok; tile += workers) {
       const TileWork work = decode_tile(p, tile);
       const int tm = work.tm, tn = work.tn;
@@ -278,7 +372,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           break;
         }
         if (leader) {
-          GG_TRACE_EVENT(0, trace_cursor, 1);
           uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
           uint8_t* b_dst = a_dst + Shape::kABytes;
           if constexpr (kCtaGroup == 1) {
@@ -290,7 +383,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tma_load_2d_pair(a_dst, &map_a, &full_bar[stage], x, row_a);
             tma_load_2d_pair(b_dst, &map_b, &full_bar[stage], x, row_b);
           }
-          GG_TRACE_EVENT(0, trace_cursor, 5);
         }
         if (++stage == kStages) {
           stage = 0;
@@ -311,7 +403,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t buffer = 0, empty_parity = 1;         // TMEM ring position
       int step = 0;                                  // MMAs issued into the open group
       bool ok = true;
-      [[maybe_unused]] int trace_cursor = 0;
       for (int tile = worker; tile < total_tiles && ok; tile += workers) {
         const TileWork work = decode_tile(p, tile);
         if constexpr (kGrouped) {
@@ -325,7 +416,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               break;
             }
             tcgen05_fence_after();
-            if (leader) GG_TRACE_EVENT(1, trace_cursor, 1);
             const bool group_start = (slab & 1) == 0;
             if (group_start) {
               if (!mbar_wait_warp(&tmem_empty_bar[buffer], empty_parity, kSiteMmaTmemEmpty,
@@ -334,23 +424,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 break;
               }
               tcgen05_fence_after();
-              if (leader) GG_TRACE_EVENT(1, trace_cursor, 2);
             }
             const uint32_t a_low = a_low_base + stage * (Shape::kStageBytes >> 4);
             const uint32_t b_low = a_low + (Shape::kABytes >> 4);
             const uint32_t tmem_d = tmem_base + buffer * BN;
             if (leader) {
-              umma_i8<kCtaGroup>(tmem_d, a_low, b_low, idesc, group_start ? 0u : 1u);
+              umma_i8<kCtaGroup>(tmem_d, a_low, b_low, idesc, (kBias || !group_start) ? 1u : 0u);
               umma_i8<kCtaGroup>(tmem_d, a_low + 2, b_low + 2, idesc, 1u);
               umma_i8<kCtaGroup>(tmem_d, a_low + 4, b_low + 4, idesc, 1u);
               umma_i8<kCtaGroup>(tmem_d, a_low + 6, b_low + 6, idesc, 1u);
-              GG_TRACE_EVENT(1, trace_cursor, 6);
               if constexpr (kCtaGroup == 1) umma_commit(&empty_bar[stage]);
               else umma_commit_pair(&empty_bar[stage], 3);
               if (!group_start) {
                 if constexpr (kCtaGroup == 1) umma_commit(&tmem_full_bar[buffer]);
                 else umma_commit_pair(&tmem_full_bar[buffer], 3);
-                GG_TRACE_EVENT(1, trace_cursor, 3);
               }
             }
             if (!group_start) {
@@ -371,7 +458,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           tcgen05_fence_after();
-          if (leader) GG_TRACE_EVENT(1, trace_cursor, 1);
           const uint32_t a_low = a_low_base + stage * (Shape::kStageBytes >> 4);
           const uint32_t b_low = a_low + (Shape::kABytes >> 4);
 #pragma unroll
@@ -384,11 +470,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                   break;
                 }
                 tcgen05_fence_after();
-                if (leader) GG_TRACE_EVENT(1, trace_cursor, 2);
               }
               if (leader) {
                 umma_i8<kCtaGroup>(tmem_base + buffer * BN, a_low + 2 * j, b_low + 2 * j, idesc,
-                                   step != 0 ? 1u : 0u);
+                                   (kBias || step != 0) ? 1u : 0u);
               }
               ++step;
               --remaining;
@@ -396,7 +481,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (leader) {
                   if constexpr (kCtaGroup == 1) umma_commit(&tmem_full_bar[buffer]);
                   else umma_commit_pair(&tmem_full_bar[buffer], 3);
-                  GG_TRACE_EVENT(1, trace_cursor, 3);
                 }
                 step = 0;
                 buffer ^= 1u;
@@ -466,9 +550,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         float* destination = scale_ring + slot * Shape::kScaleSlotFloats;
 #pragma unroll
-        for (int i = 0; i < kColumnsPerLane; ++i) destination[lane + 32 * i] = sb_now[i];
+        for (int i = 0; i < kColumnsPerLane; ++i)
+          destination[32 * i + ring_column_position(lane)] = sb_now[i];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) destination[BN + lane + 32 * i] = sa_now[i];
+        for (int i = 0; i < 4; ++i) destination[BN + 32 * i + ring_row_position(lane)] = sa_now[i];
         mbar_arrive(&scale_full_bar[slot]);
         if (++slot == Shape::kScaleSlots) {
           slot = 0;
@@ -487,7 +572,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t group_sequence = 0;
     uint32_t scale_slot = 0, scale_phase = 0;
     bool ok = true;
-    [[maybe_unused]] int trace_cursor = 0;
     OutT* c = reinterpret_cast<OutT*>(p.c);
     // A failed wait clears `ok` but the loops keep their shape, so that every thread still
     // reaches every named barrier the others wait on.
@@ -513,9 +597,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // Split-K: hand the exact INT32 group dots to the folding kernel.
         for (int g = 0; g < groups; ++g, ++group_sequence) {
           const uint32_t buffer = group_sequence & 1u;
-          if (ok && !mbar_wait(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
-                               kSiteEpilogueTmemFull, abort_flag)) {
-            ok = false;
+          if (ok) {
+            ok = mbar_wait_warp(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
+                                kSiteEpilogueTmemFull, abort_flag);
           }
           tcgen05_fence_after();
           const uint32_t taddr =
@@ -566,67 +650,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       static_assert(!kDump || kCtaGroup == 1, "split-K dump runs on single CTAs");
       const int fragment_row = lane >> 2;
-      const int fragment_col = 2 * (lane & 3);
 
+      [[maybe_unused]] uint32_t bias[16];
+      if constexpr (kBias) make_bias_block(bias);
+
+      // `ok` is the same in every lane (mbar_wait_warp votes), so the .sync.aligned TMEM
+      // instructions below always see a converged warp, also after a wait has run out.
       for (int g = 0; g < groups; ++g, ++group_sequence) {
         // This group's scales, staged by the scale warp.
-        if (ok && !mbar_test(&scale_full_bar[scale_slot], scale_phase) &&
-            !mbar_wait(&scale_full_bar[scale_slot], scale_phase, kSiteScaleFull, abort_flag)) {
-          ok = false;
+        if (ok) {
+          ok = mbar_wait_warp(&scale_full_bar[scale_slot], scale_phase, kSiteScaleFull, abort_flag);
         }
         const float* scale_slot_base = scale_ring + scale_slot * Shape::kScaleSlotFloats;
         float sa[4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) sa[r] = scale_slot_base[BN + quarter * 32 + fragment_row + 8 * r];
+        load_row_scales(scale_slot_base + BN + quarter * 32, fragment_row, sa);
         const uint32_t buffer = group_sequence & 1u;
-        if (ok && !mbar_wait(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
-                             kSiteEpilogueTmemFull, abort_flag)) {
-          ok = false;
+        if (ok) {
+          ok = mbar_wait_warp(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
+                              kSiteEpilogueTmemFull, abort_flag);
         }
         tcgen05_fence_after();
-        if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 1);
-        const float* sb_columns = scale_slot_base + col_base + fragment_col;
+        const float* sb_columns = scale_slot_base + col_base;
         const uint32_t taddr_low =
             tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN + col_base;
         const uint32_t taddr_high = taddr_low + (16u << 16);
         // Fragments alternate between the two 16-row halves of each 32-column block; the load
-        // of the next fragment is in flight while the current one is promoted.
+        // of the next fragment is in flight while the current one is promoted.  With biased
+        // accumulators every fragment is reset to the bias as soon as it has been read.
         uint32_t partial_a[16], partial_b[16];
         float2 sb[4];
-        if (ok) tmem_ld_16x256b_x4(taddr_low, partial_a);
+        if (ok) {
+          tmem_ld_16x256b_x4(taddr_low, partial_a);
 #pragma unroll
-        for (int fragment = 0; fragment < 2 * kBlocks; ++fragment) {
-          if (!ok) break;
-          const int block = fragment >> 1;
-          const int high_half = fragment & 1;
-          if (!high_half) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              sb[i] = *reinterpret_cast<const float2*>(sb_columns + block * 32 + 8 * i);
-          }
-          tmem_ld_wait();
-          if (fragment == 0 && threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 4);
-          if (fragment + 1 < 2 * kBlocks) {
-            const uint32_t next = ((fragment + 1) & 1 ? taddr_high : taddr_low) +
-                                  ((fragment + 1) >> 1) * 32;
-            if (fragment & 1) tmem_ld_16x256b_x4(next, partial_a);
-            else tmem_ld_16x256b_x4(next, partial_b);
-          } else {
-            // All of this warp's TMEM reads for the buffer are done: hand it back.
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-              if constexpr (kCtaGroup == 1) mbar_arrive(&tmem_empty_bar[buffer]);
-              else mbar_arrive_cluster(&tmem_empty_bar[buffer], 0);
+          for (int fragment = 0; fragment < 2 * kBlocks; ++fragment) {
+            const int block = fragment >> 1;
+            const int high_half = fragment & 1;
+            if (!high_half) load_column_scales(sb_columns + block * 32, lane & 3, sb);
+            tmem_ld_wait();
+            if constexpr (kBias) {
+              tmem_st_16x256b_x4((high_half ? taddr_high : taddr_low) + block * 32, bias);
+            }
+            if (fragment + 1 < 2 * kBlocks) {
+              const uint32_t next = ((fragment + 1) & 1 ? taddr_high : taddr_low) +
+                                    ((fragment + 1) >> 1) * 32;
+              if (fragment & 1) tmem_ld_16x256b_x4(next, partial_a);
+              else tmem_ld_16x256b_x4(next, partial_b);
+            } else {
+              // All of this warp's TMEM accesses for the buffer are done: hand it back.
+              if constexpr (kBias) tmem_st_wait();
+              tcgen05_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+                if constexpr (kCtaGroup == 1) mbar_arrive(&tmem_empty_bar[buffer]);
+                else mbar_arrive_cluster(&tmem_empty_bar[buffer], 0);
+              }
+            }
+            if (fragment & 1) {
+              promote_fragment<kBias>(partial_b, sa[2], sa[3], sb, &acc[2][block * 4],
+                                      &acc[3][block * 4]);
+            } else {
+              promote_fragment<kBias>(partial_a, sa[0], sa[1], sb, &acc[0][block * 4],
+                                      &acc[1][block * 4]);
             }
           }
-          if (fragment & 1) {
-            promote_fragment(partial_b, sa[2], sa[3], sb, &acc[2][block * 4], &acc[3][block * 4]);
-          } else {
-            promote_fragment(partial_a, sa[0], sa[1], sb, &acc[0][block * 4], &acc[1][block * 4]);
-          }
         }
-        if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 2);
         // Every lane has consumed the slot's values (they fed the arithmetic above).
         __syncwarp();
         if (lane == 0) mbar_arrive(&scale_empty_bar[scale_slot]);
@@ -634,13 +721,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           scale_slot = 0;
           scale_phase ^= 1u;
         }
-        if (threadIdx.x == 0) GG_TRACE_EVENT(2, trace_cursor, 3);
       }
       // The fragment layout leaves each lane with column pairs 8 apart.  A 4x4 exchange inside
       // every quad gives lane q the eight consecutive columns 8q..8q+7 of each 32-column
       // block, so that a row leaves as 16-byte stores (a quarter of the store instructions and
       // of the memory-pipe wavefronts of pair stores).
-      if (__all_sync(0xffffffffu, ok)) {
+      if (ok) {
         const int quad = lane & 3;
         const int first_row = row - row_in_cta + quarter * 32 + fragment_row;
         const bool aligned = p.c_vector_ok != 0;

@@ -53,7 +53,7 @@ struct GateUpShape {
   static constexpr int kRingFloats = 256 + 128;   // column scales then row scales of one group
   static constexpr int kScaleSlots = 4;
   static constexpr int kScaleBytes = kScaleSlots * kRingFloats * 4;
-  static constexpr int kAmaxBytes = 4 * 128 * 4;
+  static constexpr int kAmaxBytes = 2 * 4 * 128 * 4;   // two item parities x (sub, half) x 128 rows
   static constexpr int kBarrierBytes = (2 * kStages + 4 + 2 * kScaleSlots) * 8 + 16;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStashBytes + kScaleBytes +
                                     kAmaxBytes + kBarrierBytes;
@@ -104,7 +104,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   float* stash = reinterpret_cast<float*>(smem + kStages * Shape::kStageBytes);
   float* sb_ring = stash + Shape::kStashBytes / 4;
   float* amax_part = sb_ring + Shape::kScaleSlots * Shape::kRingFloats;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(amax_part + 4 * 128);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(amax_part + 2 * 4 * 128);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full_bar = empty_bar + kStages;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
@@ -145,10 +145,31 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  constexpr bool kBias = kTmemBias;
+
+  if constexpr (kBias) {
+    // Every accumulator word starts at the bias (see kAccumulatorBias): each promotion warp
+    // presets its 32 lanes of all 512 columns before the first MMA may be issued.
+    if (warp < 8) {
+      uint32_t bias[16];
+      make_bias_block(bias);
+      const uint32_t lanes = static_cast<uint32_t>((warp & 3) * 32) << 16;
+#pragma unroll
+      for (int block = 0; block < 8; ++block) {
+        const uint32_t taddr = tmem_base + lanes + (warp >> 2) * 256 + block * 32;
+        tmem_st_16x256b_x4(taddr, bias);
+        tmem_st_16x256b_x4(taddr + (16u << 16), bias);
+      }
+      tmem_st_wait();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+  }
 
   // Warps 8-11 (producer, MMA issuer, two spares) give registers to the promotion warps.
   if (warp >= 8) {
-  setmaxnreg_dec<64>();
+  setmaxnreg_dec<GG_AUX_REGS>();
   if (warp != 9) {
     // ------------------------------------------------------------ TMA producer (warp 8)
     // Three boxes per stage: 128 sorted activation rows, 128 gate and 128 up weight rows.
@@ -226,9 +247,9 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             }
             float* destination = sb_ring + slot * Shape::kRingFloats;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) destination[lane + 32 * i] = sb_next[i];
+            for (int i = 0; i < 8; ++i) destination[32 * i + ring_column_position(lane)] = sb_next[i];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) destination[BN + lane + 32 * i] = sa_next[i];
+            for (int i = 0; i < 4; ++i) destination[BN + 32 * i + ring_row_position(lane)] = sa_next[i];
             mbar_arrive(&scale_full_bar[slot]);
             if (++slot == Shape::kScaleSlots) {
               slot = 0;
@@ -272,7 +293,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             const uint32_t b_low = a_low + (Shape::kABytes >> 4);
             const uint32_t tmem_d = tmem_base + buffer * BN;
             if (leader) {
-              umma_i8<1>(tmem_d, a_low, b_low, idesc, group_start ? 0u : 1u);
+              umma_i8<1>(tmem_d, a_low, b_low, idesc, (kBias || !group_start) ? 1u : 0u);
               umma_i8<1>(tmem_d, a_low + 2, b_low + 2, idesc, 1u);
               umma_i8<1>(tmem_d, a_low + 4, b_low + 4, idesc, 1u);
               umma_i8<1>(tmem_d, a_low + 6, b_low + 6, idesc, 1u);
@@ -293,7 +314,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     }
   }
   } else {
-    setmaxnreg_inc<216>();
+    setmaxnreg_inc<GG_PROMO_REGS>();
     // ------------------------------------------------------------ promotion + SwiGLU warps
     // Fragment layout (tmem_ld_16x256b_x4): warp (quarter, half) drains TMEM lanes
     // 32*quarter.. of four 32-column blocks; a thread owns tile rows
@@ -310,6 +331,13 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     uint32_t scale_slot = 0, scale_phase = 0;
     bool ok = true;
     float4* stash4 = reinterpret_cast<float4*>(stash) + tid;   // element j at stash4[j * 256]
+    [[maybe_unused]] uint32_t bias[16];
+    if constexpr (kBias) make_bias_block(bias);
+    // The row-maximum exchange buffer alternates between two copies from one work item to the
+    // next: a warp may start the next item (and write its sub-tile 0 maxima) while its partner
+    // half is still reading this item's; the barrier of the next item keeps it from getting
+    // two items ahead.
+    uint32_t item_parity = 0;
     int block_column[4];
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
@@ -333,19 +361,18 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         }
         for (int g = 0; g < groups; ++g, ++group_sequence) {
           // This group's scales, staged by the scale warp: [0, 256) column scales by
-          // accumulator column, [256, 384) row scales by tile row.
-          if (ok && !mbar_test(&scale_full_bar[scale_slot], scale_phase) &&
-              !mbar_wait(&scale_full_bar[scale_slot], scale_phase, kSiteScaleFull, abort_flag)) {
-            ok = false;
+          // accumulator column, [256, 384) row scales by tile row (both in the order the
+          // promotion threads read them).  `ok` is the same in every lane.
+          if (ok) {
+            ok = mbar_wait_warp(&scale_full_bar[scale_slot], scale_phase, kSiteScaleFull, abort_flag);
           }
           const float* slot = sb_ring + scale_slot * Shape::kRingFloats;
           float sa[4];
-#pragma unroll
-          for (int r = 0; r < 4; ++r) sa[r] = slot[BN + quarter * 32 + fragment_row + 8 * r];
+          load_row_scales(slot + BN + quarter * 32, fragment_row, sa);
           const uint32_t buffer = group_sequence & 1u;
-          if (ok && !mbar_wait(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
-                               kSiteEpilogueTmemFull, abort_flag)) {
-            ok = false;
+          if (ok) {
+            ok = mbar_wait_warp(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
+                                kSiteEpilogueTmemFull, abort_flag);
           }
           tcgen05_fence_after();
           const uint32_t taddr_low =
@@ -353,33 +380,36 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
           const uint32_t taddr_high = taddr_low + (16u << 16);
           uint32_t partial_a[16], partial_b[16];
           float2 sb[4];
-          if (ok) tmem_ld_16x256b_x4(taddr_low + block_column[0], partial_a);
+          if (ok) {
+            tmem_ld_16x256b_x4(taddr_low + block_column[0], partial_a);
 #pragma unroll
-          for (int fragment = 0; fragment < 8; ++fragment) {
-            if (!ok) break;
-            const int block = fragment >> 1;
-            if ((fragment & 1) == 0) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                sb[i] = *reinterpret_cast<const float2*>(slot + block_column[block] + 8 * i + 2 * quad);
+            for (int fragment = 0; fragment < 8; ++fragment) {
+              const int block = fragment >> 1;
+              if ((fragment & 1) == 0) load_column_scales(slot + block_column[block], quad, sb);
+              tmem_ld_wait();
+              if constexpr (kBias) {
+                tmem_st_16x256b_x4(((fragment & 1) ? taddr_high : taddr_low) + block_column[block],
+                                   bias);
               }
-            }
-            tmem_ld_wait();
-            if (fragment + 1 < 8) {
-              const uint32_t next = ((fragment + 1) & 1 ? taddr_high : taddr_low) +
-                                    block_column[(fragment + 1) >> 1];
-              if (fragment & 1) tmem_ld_16x256b_x4(next, partial_a);
-              else tmem_ld_16x256b_x4(next, partial_b);
-            } else {
-              // All of this warp's TMEM reads for the buffer are done: hand it back.
-              tcgen05_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
-            }
-            if (fragment & 1) {
-              promote_fragment(partial_b, sa[2], sa[3], sb, &acc[2][block * 4], &acc[3][block * 4]);
-            } else {
-              promote_fragment(partial_a, sa[0], sa[1], sb, &acc[0][block * 4], &acc[1][block * 4]);
+              if (fragment + 1 < 8) {
+                const uint32_t next = ((fragment + 1) & 1 ? taddr_high : taddr_low) +
+                                      block_column[(fragment + 1) >> 1];
+                if (fragment & 1) tmem_ld_16x256b_x4(next, partial_a);
+                else tmem_ld_16x256b_x4(next, partial_b);
+              } else {
+                // All of this warp's TMEM accesses for the buffer are done: hand it back.
+                if constexpr (kBias) tmem_st_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
+              }
+              if (fragment & 1) {
+                promote_fragment<kBias>(partial_b, sa[2], sa[3], sb, &acc[2][block * 4],
+                                        &acc[3][block * 4]);
+              } else {
+                promote_fragment<kBias>(partial_a, sa[0], sa[1], sb, &acc[0][block * 4],
+                                        &acc[1][block * 4]);
+              }
             }
           }
           // Every lane has consumed the slot's values (they fed the arithmetic above).
@@ -426,7 +456,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
           row_amax = fmaxf(row_amax, __shfl_xor_sync(0xffffffffu, row_amax, 2));
           amax[r] = row_amax;
           if (quad == 0) {
-            amax_part[(sub * 2 + half) * 128 + quarter * 32 + fragment_row + 8 * r] = row_amax;
+            amax_part[((item_parity * 2 + sub) * 2 + half) * 128 + quarter * 32 + fragment_row + 8 * r] = row_amax;
           }
         }
         if (sub == 0) {
@@ -440,13 +470,13 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
           }
         } else {
           named_barrier_sync(1, 256);
-          const bool all_ok = __all_sync(0xffffffffu, ok);
+          const bool all_ok = ok;
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
             const int tile_row = quarter * 32 + fragment_row + 8 * r;
             float row_max = fmaxf(amax[r], amax_first[r]);
-            row_max = fmaxf(row_max, amax_part[(0 * 2 + (half ^ 1)) * 128 + tile_row]);
-            row_max = fmaxf(row_max, amax_part[(1 * 2 + (half ^ 1)) * 128 + tile_row]);
+            row_max = fmaxf(row_max, amax_part[((item_parity * 2 + 0) * 2 + (half ^ 1)) * 128 + tile_row]);
+            row_max = fmaxf(row_max, amax_part[((item_parity * 2 + 1) * 2 + (half ^ 1)) * 128 + tile_row]);
             const float scale = quantize_scale(row_max);
             const bool by_fma = quantize_division_is_safe(row_max);
             const float y = __frcp_rn(scale);
@@ -511,6 +541,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
           }
         }
       }
+      item_parity ^= 1u;
     }
   }
 

@@ -451,7 +451,8 @@ swiglu_quantize_kernel(const InT* __restrict__ gate_up, long long rows,
 template <typename T>
 __global__ void __launch_bounds__(256)
 combine_kernel(const T* __restrict__ expert_out, const float* __restrict__ weights,
-               const int* __restrict__ inverse, T* __restrict__ out, int top_k, int hidden) {
+               const int* __restrict__ inverse, T* __restrict__ out, int top_k, int hidden,
+               int vector_ok) {
   extern __shared__ int slot_smem[];  // [R] slots then [R] weights
   float* weight_smem = reinterpret_cast<float*>(slot_smem + top_k);
   const long long token = blockIdx.x;
@@ -461,7 +462,6 @@ combine_kernel(const T* __restrict__ expert_out, const float* __restrict__ weigh
     weight_smem[r] = slot >= 0 ? weights[token * top_k + r] : 0.0f;
   }
   __syncthreads();
-  const bool vector_ok = (hidden % 8) == 0;
   if (vector_ok) {
     for (int col = threadIdx.x * 8; col < hidden; col += blockDim.x * 8) {
       float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};

@@ -21,26 +21,13 @@ enum WaitSite : unsigned int {
   kSiteDrain = 5,
   kSiteScaleEmpty = 8,
   kSiteScaleFull = 9,
+  kSiteSelfTest = 15,
 };
 
 __device__ __forceinline__ void report_timeout(unsigned int site) {
   atomicCAS(&g_device_status[0], 0u, (site << 8) | 1u);
   atomicAdd(&g_device_status[1], 1u);
 }
-
-// Optional timeline of CTA 0 (build with -DGG_TRACE): per role a list of (tag, SM clock).
-#ifdef GG_TRACE
-__device__ long long g_trace[3 * 2048];
-__device__ __forceinline__ void trace_event(int role, int& cursor, int tag) {
-  if (blockIdx.x == 0 && cursor < 2048) {
-    g_trace[role * 2048 + cursor] = (static_cast<long long>(tag) << 56) | (clock64() & 0xffffffffffffffll);
-    ++cursor;
-  }
-}
-#define GG_TRACE_EVENT(role, cursor, tag) trace_event(role, cursor, tag)
-#else
-#define GG_TRACE_EVENT(role, cursor, tag)
-#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -97,7 +84,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta)
       "{\n\t"
       ".reg .b32 remote;\n\t"
       "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
-      "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t"
       "}" ::"r"(smem_u32(bar)), "r"(cta)
       : "memory");
 }
@@ -130,11 +117,16 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// Longest time a wait may take before the kernel gives up (nanoseconds of %globaltimer).
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
 // Bounded wait on a phase parity.  Returns false (after reporting `site`) when the
-// barrier has not flipped within about two seconds, or when another thread of the
-// CTA has already given up (*abort_flag != 0).
+// barrier has not flipped within `limit_ns`, or when another thread of the CTA has already
+// given up (*abort_flag != 0).  The clock is read only after a probe has failed and come
+// back from its suspension, every 64 such failures, so a wait that succeeds costs nothing.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int site,
-                                          volatile int* abort_flag) {
+                                          volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   const uint32_t addr = smem_u32(bar);
   uint64_t start = 0;
   for (uint32_t spin = 0;; ++spin) {
@@ -149,12 +141,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
         : "r"(addr), "r"(parity), "r"(kTryWaitSuspendNs)
         : "memory");
     if (done) return true;
-    if ((spin & 0x3ffu) == 0x3ffu) {
+    if ((spin & 0x3fu) == 0x3fu) {
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (start == 0) {
         start = now;
-      } else if (now - start > 2000000000ull) {
+      } else if (now - start > limit_ns) {
         *abort_flag = 1;
         report_timeout(site);
         return false;
@@ -166,10 +158,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
 // Warp-collective wait: every lane probes, then waits if needed; the verdict is the same in
 // all lanes.  Issuing warps stay converged this way, so that descriptor and address
 // arithmetic around their tcgen05.mma / TMA instructions runs in the uniform datapath; only
-// the issue itself is left to one elected lane.
+// the issue itself is left to one elected lane.  The promotion warps use it too: their
+// tcgen05.ld / tcgen05.wait are .sync.aligned and must see the whole warp take one path,
+// also after a wait has run out.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, unsigned int site,
-                                               volatile int* abort_flag) {
-  const bool got = mbar_test(bar, parity) || mbar_wait(bar, parity, site, abort_flag);
+                                               volatile int* abort_flag,
+                                               uint64_t limit_ns = kWaitLimitNs) {
+  const bool got = mbar_test(bar, parity) || mbar_wait(bar, parity, site, abort_flag, limit_ns);
   return __all_sync(0xffffffffu, got);
 }
 
@@ -337,6 +332,36 @@ __device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)
 
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Store counterpart of tmem_ld_16x256b_x4 (same element-to-register mapping).
+__device__ __forceinline__ void tmem_st_16x256b_x4(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Accumulator bias.  A K group's INT32 dot p satisfies |p| <= 2^22 (256 * 128 * 128), so the
+// integer 0x4B400000 + p, read as FP32, is exactly 12582912 + p (1.5 * 2^23 has unit spacing
+// up to 2^24).  The promotion warps therefore keep every accumulator word of TMEM preset to
+// kAccumulatorBias, the tensor core always accumulates onto it, and float(p) is one exact
+// FP32 subtraction (packed, two per instruction) instead of an integer-to-float conversion.
+constexpr uint32_t kAccumulatorBias = 0x4B400000u;
+constexpr float kAccumulatorBiasValue = 12582912.0f;
+
+// Sixteen registers holding the bias, for tmem_st_16x256b_x4.  The values come out of an
+// asm statement so that the compiler keeps one register block instead of rebuilding it in
+// front of every store.
+__device__ __forceinline__ void make_bias_block(uint32_t (&r)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) asm volatile("mov.u32 %0, %1;" : "=r"(r[i]) : "n"(0x4B400000));
 }
 
 // ---------------------------------------------------------------- misc

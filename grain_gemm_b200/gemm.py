@@ -24,6 +24,8 @@ def _check_backend(backend):
         raise ValueError("backend must be 'auto', 'triton', 'cuda', or 'cutlass'")
 
 
+# Validation contract restated from the reference's src/grain_gemm/gemm.py:13-50 (Apache-2.0):
+# same checks, order, exception types and messages, so callers and their tests port unchanged.
 def _validate(a, b, scale_a, scale_b, group_size, output_dtype):
     if type(group_size) is not int or group_size not in (32, 64, 128, 256):
         raise ValueError("group_size must be one of 32, 64, 128, or 256")

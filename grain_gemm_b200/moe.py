@@ -28,6 +28,8 @@ TENSOR_CORE_TILE_ROWS = 128
 CUDA_CORE_TILE_ROWS = 32
 
 
+# Validation contract (_stride, _validate) restated from the reference's
+# src/grain_gemm/moe.py:7-93 (Apache-2.0): same checks, order, exception types and messages.
 def _stride(shape, column_major=False):
     if column_major:
         e, k, n = shape

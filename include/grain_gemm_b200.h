@@ -219,9 +219,20 @@ int gg_moe_combine(const void* expert_out, const void* weights, const void* inve
 
 /*
  * Reads (and clears) the device status word that kernels set when one of their bounded
- * waits ran out.  Synchronises `stream`.  *status = 0 when every kernel completed normally.
+ * waits ran out.  Synchronises `stream`.  *status = 0 when every kernel completed normally;
+ * otherwise (site << 8) | 1 with `site` naming the wait that gave up first.
  */
 int gg_device_status(int* status, void* stream);
+
+/*
+ * Self-test of that mechanism (no counterpart in the reference, whose device waits are
+ * unbounded): launches one warp that waits, with the kernels' own bounded wait, on a barrier
+ * nothing ever completes.  The wait gives up after limit_ns nanoseconds (1 .. 100 000 000), the
+ * kernel returns normally, *result (a device int) is 0 and gg_device_status then reports
+ * GG_SELFTEST_WAIT_STATUS once.  Nothing traps or hangs: the wait is bounded by construction.
+ */
+#define GG_SELFTEST_WAIT_STATUS ((15 << 8) | 1)
+int gg_selftest_wait_timeout(long long limit_ns, void* result, void* stream);
 
 #ifdef __cplusplus
 }

@@ -23,7 +23,8 @@ def worker(rank, world, port, results):
         torch.cuda.set_device(rank)
         device = torch.device("cuda", rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
-        from grain_gemm_b200 import _loader, bench_moe, distributed, moe
+        import bench_moe
+        from grain_gemm_b200 import _loader, distributed, moe
         bench_moe.CONFIGS["ep_test"] = dict(tokens=768, hidden=1024, inter=512, experts=16,
                                             top_k=4, layout="split", biased=True)
         local = bench_moe.make_case("ep_test", device, rank=rank, world=world)

@@ -192,7 +192,7 @@ def test_closed_form_constant_inputs(gg):
 
 
 def test_base_config_and_ragged_k(gg):
-    # BASELINE configuration 1 (256 x 4096 x 4096, G256, FP32) and the ragged K = 4000 case.
+    # The CPU-runnable base case (256 x 4096 x 4096, G256, FP32) and the ragged K = 4000 case.
     for (m, n, k), dtype, scale in (((256, 4096, 4096), torch.float32, "uniform"),
                                     ((512, 4096, 4000), torch.bfloat16, "lognormal")):
         tensors = linear_case(m, n, k, 256, seed=2026, scale=scale)

@@ -78,7 +78,7 @@ def test_tile_list(moe):
 
 def make_case(tokens, hidden, inter, experts, top_k, *, seed=2026, layout="split",
               dtype=torch.bfloat16, biased=False, mask=False, ids_dtype=torch.int64):
-    """Seeded synthetic MoE case with the value distributions of the BASELINE configurations."""
+    """Seeded synthetic MoE case: uniform INT8 values, uniform positive scales, softmax top-k."""
     gen = torch.Generator().manual_seed(seed)
     x = torch.randint(-127, 128, (tokens, hidden), dtype=torch.int8, generator=gen)
     scale_x = (0.5 + torch.rand((tokens, hidden // 256), generator=gen)) / 127
@@ -280,7 +280,7 @@ def test_baseline_config_5_large_sampled_tokens_and_properties(moe):
     """T=16384, H=7168, I=2048, E=256, top-8 is far beyond the CPU oracle: check sampled tokens
     against it (on the experts those tokens use) and two size-independent properties:
     doubling every routing weight doubles the output exactly, and zero weights give zero."""
-    from grain_gemm_b200 import bench_moe
+    import bench_moe
 
     case = bench_moe.make_case("large", torch.device("cuda"))
     out = moe.moe_ffn(**case)
