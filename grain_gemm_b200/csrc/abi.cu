@@ -17,7 +17,7 @@
 
 namespace gg {
 
-constexpr int kAbiVersion = 2;
+constexpr int kAbiVersion = 3;
 
 // ---------------------------------------------------------------- host helpers
 
@@ -322,6 +322,24 @@ static int run_gemm(const GemmArgs& g, int variant, cudaStream_t stream, void* w
   return launch_gemm_tc(g, variant, stream);
 }
 
+// Row-gather mode of the fused Gate/Up kernel (the shipped mode): the producer fetches token
+// rows from x[T, H] by TMA row gathers and the scratch holds only the SiLU table.  With 0 the
+// rows are first copied into sorted order (kept for measurements).
+#ifndef GG_GATE_UP_GATHER
+#define GG_GATE_UP_GATHER 1
+#endif
+
+template <typename RoundT>
+static int launch_gate_up_tc(const CUtensorMap& map_x, const CUtensorMap& map_w,
+                             const GateUpParams& p, int grid, cudaStream_t stream) {
+  auto kernel = moe_gate_up_tc_kernel<RoundT, GG_GATE_UP_GATHER != 0>;
+  const cudaError_t error = cudaFuncSetAttribute(
+      kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GateUpShape::kSmemBytes);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  kernel<<<grid, 384, GateUpShape::kSmemBytes, stream>>>(map_x, map_w, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // One warp waits, with the kernels' own bounded wait, on a barrier that nothing ever
 // completes: the wait gives up after `limit_ns`, records (kSiteSelfTest << 8) | 1 in the device
 // status word and the kernel returns normally.  *result = 1 if the wait reported success.
@@ -519,6 +537,10 @@ int gg_moe_route_noalloc(const void* ids, int ids_are_i64, const void* mask, int
   if (tokens < 0 || top_k <= 0 || experts <= 0) return static_cast<int>(cudaErrorInvalidValue);
   const size_t needed = gg_moe_route_workspace_bytes(tokens, top_k, experts);
   if (needed > kStaticRouteScratchInts * sizeof(int)) return GG_STATUS_STATIC_SCRATCH_TOO_SMALL;
+  if (!counts || !offsets || !statistics ||
+      (static_cast<long long>(tokens) * top_k > 0 && (!ids || !effective_ids || !order || !inverse))) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
   int* scratch = nullptr;
   const int status = static_route_scratch(&scratch);
   if (status) return status;
@@ -547,16 +569,26 @@ int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, 
   return static_cast<int>(cudaGetLastError());
 }
 
-// Tensor-core path: [activation rows in sorted order | their scales | SiLU table].
 size_t gg_moe_gate_up_scratch_bytes(int assignments, int hidden, int intermediate, int tile_rows) {
   const size_t slots = static_cast<size_t>(assignments > 0 ? assignments : 0);
   if (tile_rows == 128) {
+    const size_t table = 65536 * sizeof(float);
+    if (GG_GATE_UP_GATHER) return table;
     const size_t rows = slots * static_cast<size_t>(hidden > 0 ? hidden : 0);
     const size_t scales = slots * static_cast<size_t>(hidden > 0 ? hidden / 256 : 0) * 4;
     return ((rows + 255) & ~static_cast<size_t>(255)) + ((scales + 255) & ~static_cast<size_t>(255)) +
-           65536 * sizeof(float);
+           table;
   }
   return slots * 2 * intermediate * 2;
+}
+
+int gg_moe_silu_table(void* table, int out_dtype, void* stream_ptr) {
+  if (!table || (out_dtype != GG_OUT_BF16 && out_dtype != GG_OUT_FP16)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  gg::silu_table_kernel<<<256, 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      static_cast<float*>(table), out_dtype == GG_OUT_FP16 ? 1 : 0);
+  return static_cast<int>(cudaGetLastError());
 }
 
 int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const void* scale_w1,
@@ -577,33 +609,41 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
         !gg::aligned16(gate_up_scratch)) {
       return static_cast<int>(cudaErrorInvalidValue);
     }
-    // Stage 2a: activation rows and their scales in sorted-slot order.
     uint8_t* scratch = static_cast<uint8_t*>(gate_up_scratch);
-    int8_t* sorted_x = reinterpret_cast<int8_t*>(scratch);
-    const size_t row_bytes = (static_cast<size_t>(slots) * hidden + 255) & ~static_cast<size_t>(255);
-    float* sorted_scale = reinterpret_cast<float*>(scratch + row_bytes);
-    const size_t scale_bytes =
-        (static_cast<size_t>(slots) * (hidden / 256) * 4 + 255) & ~static_cast<size_t>(255);
-    float* silu_table = reinterpret_cast<float*>(scratch + row_bytes + scale_bytes);
-    {
+    gg::GateUpParams p = {};
+    CUtensorMap map_x, map_w;
+    int status;
+    if (GG_GATE_UP_GATHER) {
+      p.silu_table = reinterpret_cast<float*>(scratch);
+      p.row_scale = static_cast<const float*>(scale_x);
+      status = gg::encode_int8_rows(&map_x, x, tokens, hidden, hidden, 1);
+    } else {
+      // Activation rows and their scales in sorted-slot order first.
+      int8_t* sorted_x = reinterpret_cast<int8_t*>(scratch);
+      const size_t row_bytes = (static_cast<size_t>(slots) * hidden + 255) & ~static_cast<size_t>(255);
+      float* sorted_scale = reinterpret_cast<float*>(scratch + row_bytes);
+      const size_t scale_bytes =
+          (static_cast<size_t>(slots) * (hidden / 256) * 4 + 255) & ~static_cast<size_t>(255);
+      p.silu_table = reinterpret_cast<float*>(scratch + row_bytes + scale_bytes);
+      p.row_scale = sorted_scale;
       const long long blocks = (slots + 7) / 8;
       const int limit = gg::sm_count() * 8;
       gg::gather_rows_kernel<<<static_cast<int>(blocks < limit ? blocks : limit), 256, 0, stream>>>(
           static_cast<const int8_t*>(x), static_cast<const float*>(scale_x),
           static_cast<const long long*>(order), static_cast<const int*>(offsets), experts, top_k,
-          hidden, sorted_x, sorted_scale, silu_table, out_dtype == GG_OUT_FP16 ? 1 : 0);
+          hidden, sorted_x, sorted_scale);
       const cudaError_t error = cudaGetLastError();
       if (error != cudaSuccess) return static_cast<int>(error);
+      status = gg::encode_int8_rows(&map_x, sorted_x, slots, hidden, hidden, 128);
     }
-    CUtensorMap map_x, map_w;
-    int status = gg::encode_int8_rows(&map_x, sorted_x, slots, hidden, hidden, 128);
+    if (status) return status;
+    status = gg_moe_silu_table(const_cast<float*>(p.silu_table), out_dtype, stream_ptr);
     if (status) return status;
     status = gg::encode_int8_rows(&map_w, w1, static_cast<long long>(experts) * 2 * intermediate,
                                   hidden, hidden, 128);
     if (status) return status;
-    gg::GateUpParams p = {};
-    p.sorted_scale = sorted_scale;
-    p.silu_table = silu_table;
+    p.order = static_cast<const long long*>(order);
+    p.top_k = top_k;
     p.scale_w = static_cast<const float*>(scale_w1);
     p.expert_offsets = static_cast<const int*>(offsets);
     p.tile_expert = static_cast<const int*>(tile_expert);
@@ -614,21 +654,8 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
     p.max_tiles = tile_capacity; p.interleaved = interleaved;
     const long long items = static_cast<long long>(tile_capacity) * (intermediate / 256);
     const int grid = static_cast<int>(items < gg::sm_count() ? items : gg::sm_count());
-    cudaError_t error;
-    if (out_dtype == GG_OUT_BF16) {
-      auto kernel = gg::moe_gate_up_tc_kernel<__nv_bfloat16>;
-      error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   gg::GateUpShape::kSmemBytes);
-      if (error != cudaSuccess) return static_cast<int>(error);
-      kernel<<<grid, 384, gg::GateUpShape::kSmemBytes, stream>>>(map_x, map_w, p);
-    } else {
-      auto kernel = gg::moe_gate_up_tc_kernel<__half>;
-      error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   gg::GateUpShape::kSmemBytes);
-      if (error != cudaSuccess) return static_cast<int>(error);
-      kernel<<<grid, 384, gg::GateUpShape::kSmemBytes, stream>>>(map_x, map_w, p);
-    }
-    return static_cast<int>(cudaGetLastError());
+    if (out_dtype == GG_OUT_BF16) return gg::launch_gate_up_tc<__nv_bfloat16>(map_x, map_w, p, grid, stream);
+    return gg::launch_gate_up_tc<__half>(map_x, map_w, p, grid, stream);
   }
   if (tile_rows != gg::kSimtTile || !gate_up_scratch) return static_cast<int>(cudaErrorInvalidValue);
   // CUDA-core path: ragged gathered GEMM into the scratch matrix, then SwiGLU + requantisation.

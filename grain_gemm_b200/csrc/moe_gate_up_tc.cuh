@@ -33,7 +33,9 @@
 namespace gg {
 
 struct GateUpParams {
-  const float* sorted_scale;  // [S, H/256] row scales in sorted-slot order
+  const float* row_scale;     // gathered: scale_x [T, H/256]; pre-sorted: [S, H/256] by sorted slot
+  const long long* order;     // [S] sorted slot -> flattened assignment (gathered mode)
+  int top_k;                  // assignment / top_k = token
   const float* silu_table;    // [65536] silu of every value of the output type, by bit pattern
   const float* scale_w;       // [E, H/256, 2I]
   const int* expert_offsets;  // [E+1]
@@ -88,7 +90,16 @@ __device__ __forceinline__ float2 unpack_pair(uint32_t packed) {
   }
 }
 
-template <typename RoundT>
+// Token row of the tile row `row` (gathered mode); rows past the expert's last one read token 0,
+// whose data only feeds accumulator rows that are never stored.
+__device__ __forceinline__ int gate_up_source_row(const GateUpParams& p, int row, int row_end) {
+  return row < row_end ? static_cast<int>(p.order[row] / p.top_k) : 0;
+}
+
+// kGather: map_x covers the original activations x[T, H] and the producer fetches each tile's
+// rows by token index with TMA row gathers (no copy of the rows in sorted order exists);
+// otherwise map_x covers a pre-sorted copy [S, H] and the tile is one tiled box.
+template <typename RoundT, bool kGather>
 __global__ void __launch_bounds__(384, 1)
 moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                       const __grid_constant__ CUtensorMap map_w, const GateUpParams p) {
@@ -173,7 +184,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   if (warp != 9) {
     // ------------------------------------------------------------ TMA producer (warp 8)
     // Three boxes per stage: 128 sorted activation rows, 128 gate and 128 up weight rows.
-    // The warp walks the ring converged; one elected lane issues.  Warp 11 idles.
+    // The warp walks the ring converged; one elected lane issues the tiled loads.  Warp 11 idles.
     if (warp == 8) {
       const bool leader = elect_one();
       uint32_t stage = 0, phase = 0;
@@ -182,6 +193,12 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         int tile, jg, expert;
         if (!gate_up_item(p, item, channel_groups, tile, jg, expert)) continue;
         const int row0 = p.tile_row[tile];
+        [[maybe_unused]] int source[4];   // token rows of tile rows 4 * lane .. 4 * lane + 3
+        if constexpr (kGather) {
+          const int row_end = p.expert_offsets[expert + 1];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) source[i] = gate_up_source_row(p, row0 + 4 * lane + i, row_end);
+        }
         for (int sub = 0; sub < 2 && ok; ++sub) {
           const int channel0 = jg * 256 + sub * 128;
           const int w_base = expert * 2 * p.intermediate;
@@ -192,13 +209,18 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
               ok = false;
               break;
             }
+            uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
+            uint8_t* b_dst = a_dst + Shape::kABytes;
             if (leader) {
-              uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
-              uint8_t* b_dst = a_dst + Shape::kABytes;
               mbar_expect_tx(&full_bar[stage], Shape::kStageBytes);
-              tma_load_2d(a_dst, &map_x, &full_bar[stage], x, row0);
+              if constexpr (!kGather) tma_load_2d(a_dst, &map_x, &full_bar[stage], x, row0);
               tma_load_2d(b_dst, &map_w, &full_bar[stage], x, row_gate);
               tma_load_2d(b_dst + 128 * 128, &map_w, &full_bar[stage], x, row_up);
+            }
+            if constexpr (kGather) {
+              // Every lane fetches its four rows: 32 gathers of 512 bytes fill the A tile.
+              tma_gather4_rows(a_dst + lane * 512, &map_x, &full_bar[stage], x, source[0], source[1],
+                               source[2], source[3]);
             }
             if (++stage == kStages) {
               stage = 0;
@@ -220,6 +242,12 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         const int row0 = p.tile_row[tile];
         const int row_end = p.expert_offsets[expert + 1];
         const float* sb_base = p.scale_w + static_cast<long long>(expert) * groups * 2 * p.intermediate;
+        long long scale_row[4];   // row of row_scale for tile rows lane + 32 * i
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = row0 + lane + 32 * i;
+          scale_row[i] = kGather ? gate_up_source_row(p, r, row_end) : r;
+        }
         for (int sub = 0; sub < 2 && ok; ++sub) {
           const int channel0 = jg * 256 + sub * 128;
           float sb_next[8], sa_next[4];
@@ -234,7 +262,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int r = row0 + lane + 32 * i;
-              sa_next[i] = r < row_end ? p.sorted_scale[static_cast<long long>(r) * groups + g] : 0.0f;
+              sa_next[i] = r < row_end ? p.row_scale[scale_row[i] * groups + g] : 0.0f;
             }
           };
           fetch(0);

@@ -206,27 +206,29 @@ moe_tiles_kernel(const int* __restrict__ offsets, int experts, int tile_rows, in
 
 // ------------------------------------------------------------------ SwiGLU + requantisation
 
-// Activation rows and their scales in sorted-slot order, for the valid slots only:
-// sorted_x[slot, :] = x[order[slot] / top_k, :] and likewise for the row scales, so that the
-// fused Gate/Up kernel can fetch whole 128-row operand tiles by TMA.  One warp per slot; a
-// row is `hidden` bytes (a multiple of 256) moved as 16-byte vectors.
-//
-// The same launch fills the SiLU table of the fused kernel: gate values reach SwiGLU rounded to
-// the 16-bit output type, so silu(gate) = div_rn(gate, 1 + exp(-gate)) has only 65536 possible
+// SiLU table of the fused Gate/Up kernel: gate values reach SwiGLU rounded to the 16-bit
+// output type, so silu(gate) = div_rn(gate, 1 + exp(-gate)) has only 65536 possible
 // arguments.  Entry b holds the result for the value whose bit pattern is b, computed here with
 // exactly the operations of swiglu_value, hence bit-identical to evaluating the formula
 // (the idea of the reference's experiments/thor_interleaved_mega/exact_silu_lut.cuh:1-36).
 __global__ void __launch_bounds__(256)
+silu_table_kernel(float* __restrict__ silu_table, int half_output) {
+  const int bits = blockIdx.x * 256 + threadIdx.x;
+  if (bits >= 65536) return;
+  const float gate = half_output ? __half2float(__ushort_as_half(static_cast<unsigned short>(bits)))
+                                 : __uint_as_float(static_cast<uint32_t>(bits) << 16);
+  silu_table[bits] = __fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate)));
+}
+
+// Activation rows and their scales in sorted-slot order, for the valid slots only:
+// sorted_x[slot, :] = x[order[slot] / top_k, :] and likewise for the row scales (the
+// pre-sorted mode of the fused Gate/Up kernel, kept for measurements against the row-gather
+// mode).  One warp per slot; a row is `hidden` bytes (a multiple of 256) moved as 16-byte vectors.
+__global__ void __launch_bounds__(256)
 gather_rows_kernel(const int8_t* __restrict__ x, const float* __restrict__ scale_x,
                    const long long* __restrict__ order, const int* __restrict__ offsets,
                    int experts, int top_k, int hidden, int8_t* __restrict__ sorted_x,
-                   float* __restrict__ sorted_scale, float* __restrict__ silu_table,
-                   int half_output) {
-  for (int bits = blockIdx.x * 256 + threadIdx.x; bits < 65536; bits += gridDim.x * 256) {
-    const float gate = half_output ? __half2float(__ushort_as_half(static_cast<unsigned short>(bits)))
-                                   : __uint_as_float(static_cast<uint32_t>(bits) << 16);
-    silu_table[bits] = __fdiv_rn(gate, __fadd_rn(1.0f, expf(-gate)));
-  }
+                   float* __restrict__ sorted_scale) {
   const int valid = offsets[experts];
   const int lane = threadIdx.x & 31;
   const int groups = hidden / 256;

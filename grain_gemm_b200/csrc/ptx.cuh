@@ -185,6 +185,22 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// Row gather: four rows y0..y3 of a 2-D tensor (128 bytes each at byte column x; the tensor map
+// has a box of 128 bytes x 1 row) land as four consecutive 128-byte rows at smem_dst, with the
+// tensor map's swizzle applied by shared-memory address, so 32 such copies at 512-byte steps
+// fill a 128-row operand tile exactly like one tiled load of 128 consecutive rows.
+// A per-CTA load: no multicast.  x must be a multiple of 16.
+__device__ __forceinline__ void tma_gather4_rows(void* smem_dst, const CUtensorMap* map,
+                                                 uint64_t* bar, int32_t x, int32_t y0, int32_t y1,
+                                                 int32_t y2, int32_t y3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y0), "r"(y1), "r"(y2),
+      "r"(y3)
+      : "memory");
+}
+
 // Pair variant: the data lands in this CTA's shared memory, the bytes are counted on the
 // barrier of the pair's leader CTA (rank 0) at the same offset.  Each CTA issues its own
 // load for its own half of the tile.

@@ -176,16 +176,26 @@ int gg_quantize_rows(const void* x, int in_dtype, long long rows, int width, int
                      void* q, void* s, void* stream);
 
 /*
+ * Fills table[65536] (fp32, device) with silu(v) = v / (1 + exp(-v)) for every value v of
+ * out_dtype (GG_OUT_BF16 or GG_OUT_FP16), indexed by v's 16-bit pattern, computed with the
+ * operations of the SwiGLU formula itself (expf, one correctly rounded division).  The fused
+ * Gate/Up kernel looks silu up here; gg_moe_gate_up fills its own copy on every call, this
+ * entry point exposes the table to tests and to callers that want to inspect it.  The idea is
+ * the reference's experiments/thor_interleaved_mega/exact_silu_lut.cuh:1-36.
+ */
+int gg_moe_silu_table(void* table, int out_dtype, void* stream);
+
+/*
  * Gate/Up projection + rounding to out_dtype + SwiGLU + G256 requantisation over the sorted
  * slots: q[S,I] int8 and s[S,I/256] fp32; rows are gathered from x[T,H] by order[slot] / R.
  * w1: Linear [E,2I,H] contiguous int8; scale_w1: [E,H/256,2I] fp32.  interleaved != 0 means
  * the 2I dimension is ordered [g0,u0,g1,u1,...].  tile_rows must be the value given to
  * gg_moe_tiles: 128 selects the fused tensor-core kernel (needs 16-byte aligned x and w1),
  * 32 the CUDA-core path.  gate_up_scratch must hold gg_moe_gate_up_scratch_bytes() bytes
- * (16-byte aligned): for the fused kernel the activation rows [S,H] and their scales in
- * sorted-slot order, which a small copy kernel fills first so that all operand tiles arrive
- * by TMA, plus a 256 KiB table of silu over every value of out_dtype that the same kernel
- * computes with the formula; for the CUDA-core path the [S,2I] gate/up matrix of out_dtype.
+ * (16-byte aligned): for the fused kernel the 256 KiB SiLU table only - the kernel reads the
+ * original x and scale_x rows by token index (TMA row gathers straight into shared memory),
+ * there is no copy of the activations in expert order; for the CUDA-core path the [S,2I]
+ * gate/up matrix of out_dtype.
  * Replaces ragged_gemm + swiglu_quantize (src/grain_gemm/moe.py:298-304) and
  * grain_moe_gather_launch / grain_moe_interleaved_launch
  * (csrc/sm110/int8_g256_moe_gather.cu:380, int8_g256_moe_interleaved.cu:372).

@@ -108,19 +108,38 @@ def route(topk_ids, num_experts, token_mask=None):
                   tokens, top_k, num_experts)
 
 
-def swiglu_quantize(gate_up, valid_rows=None, gate_up_layout="split"):
+def silu(values):
+    """``v / (1 + expf(-v))`` in FP32 with the host C library's ``expf``
+    (the SwiGLU formula of ``src/grain_gemm/kernels/moe.py:594``)."""
+    source = values.float().contiguous()
+    out = torch.empty_like(source)
+    _lib().oracle_silu.restype = None
+    _lib().oracle_silu(_p(source), _p(out), _i64(source.numel()))
+    return out
+
+
+def swiglu_quantize(gate_up, valid_rows=None, gate_up_layout="split", silu_table=None):
     """SwiGLU + G256 requantisation; restates ``src/grain_gemm/kernels/moe.py:564-601``.
 
     ``gate_up`` is ``[rows, 2I]`` in BF16/FP16/FP32 (the already rounded GEMM output).
+    ``silu_table`` (65536 FP32 values indexed by the 16-bit pattern of ``gate_up``'s dtype)
+    replaces the evaluation of ``gate / (1 + expf(-gate))`` by a lookup.
     """
     rows, twice = gate_up.shape
     inter = twice // 2
     values = gate_up.float().contiguous()
     q = torch.empty((rows, inter), dtype=torch.int8)
     s = torch.empty((rows, inter // 256), dtype=torch.float32)
+    table = None
+    if silu_table is not None:
+        if gate_up.dtype not in (torch.bfloat16, torch.float16):
+            raise ValueError("a SiLU table needs 16-bit gate/up values")
+        table = silu_table.float().contiguous()
+        assert table.numel() == 65536
     status = _lib().oracle_swiglu_quantize(
         _p(values), _i64(rows), _i64(rows if valid_rows is None else valid_rows), _i64(inter),
-        ctypes.c_int(int(gate_up_layout == "interleaved")), _p(q), _p(s))
+        ctypes.c_int(int(gate_up_layout == "interleaved")), _p(q), _p(s), _p(table),
+        ctypes.c_int(_OUT_KIND[gate_up.dtype] if table is not None else 0))
     if status:
         raise RuntimeError(f"oracle_swiglu_quantize failed with status {status}")
     return q, s
@@ -196,7 +215,7 @@ def combine(expert_output, topk_weights, routes, output_dtype):
 
 def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *, scale_x,
             scale_gate_up, scale_down, token_mask=None, output_dtype=torch.bfloat16,
-            gate_up_layout="split", return_stages=False):
+            gate_up_layout="split", return_stages=False, silu_table=None):
     """Full pre-routed INT8 G256 MoE FFN; stage order of ``src/grain_gemm/moe.py:296-346``.
 
     ``w_gate_up`` ``[E,H,2I]`` and ``w_down`` ``[E,I,H]`` are the logical (transposed)
@@ -209,7 +228,7 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *, scale_x
     w2 = w_down.transpose(-2, -1).contiguous()
     gate_up = ragged_gemm(hidden_states, w1, scale_x, scale_gate_up, routes,
                           output_dtype, source_is_token=True)
-    qh, sh = swiglu_quantize(gate_up, valid, gate_up_layout)
+    qh, sh = swiglu_quantize(gate_up, valid, gate_up_layout, silu_table)
     expert_out = ragged_gemm(qh, w2, sh, scale_down, routes, output_dtype,
                              source_is_token=False)
     out = combine(expert_out, topk_weights, routes, output_dtype)

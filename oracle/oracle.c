@@ -46,7 +46,12 @@
 #include <omp.h>
 #endif
 
-int oracle_abi_version(void) { return 1; }
+int oracle_abi_version(void) { return 2; }
+
+/* silu(v) = v / (1 + expf(-v)) for n values, with the host C library's expf. */
+void oracle_silu(const float* in, float* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) out[i] = in[i] / (1.0f + expf(-in[i]));
+}
 
 int oracle_threads(void) {
 #ifdef _OPENMP
@@ -209,9 +214,27 @@ int oracle_route(const void* ids, int ids_is_i64, const uint8_t* mask,
  * otherwise gate = column j, up = column I + j.
  * q: [rows, I] int8; s: [rows, I/256] FP32.
  */
+/*
+ * silu_table (optional): 65536 values of silu indexed by the gate's 16-bit pattern in the
+ * type named by table_kind (1 = bf16, 2 = fp16).  The gate values handed in are already
+ * rounded to that type, so the lookup is exact.  With a table the function evaluates
+ * silu by lookup instead of gate / (1 + expf(-gate)); tests pass the table the CUDA library
+ * computes with the same formula on the GPU, which removes the one place where host and
+ * device arithmetic (expf) can differ in the last bit.
+ */
+static inline uint32_t gate_bits(float gate, int table_kind) {
+  if (table_kind == 1) return f2u(gate) >> 16;
+  _Float16 h = (_Float16)gate;
+  uint16_t bits;
+  memcpy(&bits, &h, 2);
+  return bits;
+}
+
 int oracle_swiglu_quantize(const float* gate_up, int64_t rows, int64_t valid_rows,
-                           int64_t I, int interleaved, int8_t* q, float* s) {
+                           int64_t I, int interleaved, int8_t* q, float* s,
+                           const float* silu_table, int table_kind) {
   if (I % 256) return 1;
+  if (silu_table && table_kind != 1 && table_kind != 2) return 1;
   int64_t groups = I / 256;
 #pragma omp parallel for schedule(static)
   for (int64_t r = 0; r < rows; ++r) {
@@ -228,8 +251,13 @@ int oracle_swiglu_quantize(const float* gate_up, int64_t rows, int64_t valid_row
         int64_t c = g * 256 + j;
         float gate = gate_up[r * 2 * I + (interleaved ? 2 * c : c)];
         float up = gate_up[r * 2 * I + (interleaved ? 2 * c + 1 : I + c)];
-        float denom = 1.0f + expf(-gate);
-        float silu = gate / denom;
+        float silu;
+        if (silu_table) {
+          silu = silu_table[gate_bits(gate, table_kind)];
+        } else {
+          float denom = 1.0f + expf(-gate);
+          silu = gate / denom;
+        }
         h[j] = silu * up;
         float v = fabsf(h[j]);
         if (v > amax || v != v) amax = v;

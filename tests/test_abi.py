@@ -49,6 +49,24 @@ def test_host_side_size_queries(library):
     assert library.gg_moe_route_workspace_bytes(512, 8, 128) == chunks * 130 * 4
 
 
+def test_null_pointers_are_rejected_before_any_launch(library):
+    """Argument errors come back as cudaErrorInvalidValue (1) from the host-side checks, for
+    the single-CTA routing path too (it once reached its kernel with NULL outputs)."""
+    null = ctypes.c_void_p(0)
+    fake = ctypes.c_void_p(256)     # never dereferenced: the call fails on the NULL arguments
+    for tokens, top_k in ((4, 2), (1024, 1), (2048, 8)):
+        assert library.gg_moe_route(null, 0, null, tokens, top_k, 8, fake, fake, fake, fake, fake,
+                                    fake, null, 0, null) == 1
+        assert library.gg_moe_route(fake, 0, null, tokens, top_k, 8, fake, null, fake, fake, fake,
+                                    fake, null, 0, null) == 1
+        assert library.gg_moe_route_noalloc(fake, 0, null, tokens, top_k, 8, fake, fake, null, fake,
+                                            fake, fake, null) == 1
+    assert library.gg_moe_combine(null, fake, fake, fake, 4, 2, 256, 1, null) == 1
+    assert library.gg_selftest_wait_timeout(0, fake, null) == 1
+    assert library.gg_moe_silu_table(null, 1, null) == 1
+    assert library.gg_moe_silu_table(fake, 0, null) == 1
+
+
 def test_stale_library_is_refused(library, monkeypatch):
     monkeypatch.setattr(build, "source_hashes", lambda: {"abi.cu": "different"})
     _loader.library.cache_clear()

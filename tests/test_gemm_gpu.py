@@ -238,6 +238,28 @@ def test_full_size_linearity_property(gg):
     assert torch.equal(out[rows][:, cols].cpu(), expected)
 
 
+@pytest.mark.parametrize("g", [32, 64, 128, 256])
+@pytest.mark.parametrize("m", [1, 16, 128, 1024, 8192])
+def test_sweep_k8192_n8192_sampled_rows_bit_exact(gg, g, m):
+    """The sweep G in {32, 64, 128, 256} x M in {1, 16, 128, 1024, 8192} at K = N = 8192 with
+    lognormal scales, BF16 and FP32 outputs, whichever variant `auto` picks for the shape:
+    sampled rows (all of them for M <= 16) over all 8192 columns against the oracle."""
+    n = k = 8192
+    gen = torch.Generator(device="cuda").manual_seed(2026 + g + m)
+    a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda", generator=gen)
+    w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda", generator=gen)
+    q = k // g
+    sa = torch.exp(-5 + 0.5 * torch.randn((m, q), device="cuda", generator=gen))
+    sb = torch.exp(-5 + 0.5 * torch.randn((q, n), device="cuda", generator=gen))
+    rows = torch.arange(m) if m <= 16 else torch.tensor(sorted({0, 1, 127, m // 2 + 5, m - 129, m - 1}))
+    w_cpu, sb_cpu = w.cpu(), sb.cpu()
+    a_rows, sa_rows = a[rows.cuda()].cpu(), sa[rows.cuda()].cpu()
+    for dtype in (torch.bfloat16, torch.float32):
+        out = gg.int8_gemm(a, w.t(), sa, sb, group_size=g, output_dtype=dtype)
+        expected = oracle.int8_gemm(a_rows, w_cpu.t(), sa_rows, sb_cpu, g, dtype)
+        assert torch.equal(out[rows.cuda()].cpu(), expected), (g, m, dtype)
+
+
 def test_large_row_major_b_is_repacked_for_the_tensor_cores(gg):
     """A contiguous [K, N] B (N fastest) must not fall off a performance cliff: it is copied
     to K-contiguous storage once and gives the same bits as the Linear-format view."""

@@ -1,10 +1,13 @@
 """Parity of the CUDA MoE stages (through the C ABI) with the CPU oracle and golden fixtures.
 
-Routing metadata and the INT8/INT32 parts are bit-exact.  The fused Gate/Up stage contains
-expf, which differs between CUDA and the host C library in the last bit, so quantised
-activations may move by one step on a rounding boundary: the stage test bounds that, and the
-Down and combine stages are checked bit-exactly on the CUDA path's own quantised activations.
-Final outputs: rtol 1e-3 / atol 1e-2 after BF16/FP16 rounding.
+Every stage is compared bit for bit: routing metadata, the quantised activations and their
+scales, the Down projection and the combine.  The one place where host and device arithmetic
+can differ is ``expf`` inside SiLU.  The CUDA path evaluates SiLU once per 16-bit gate pattern
+into a 65536-entry table (``gg_moe_silu_table``); ``test_silu_table_against_host_formula``
+compares that table with the host formula entry by entry and lists the patterns that differ,
+and the stage tests hand the GPU's table to the oracle, so that everything downstream of it
+must agree exactly.  Final outputs are also checked against the table-free oracle at
+rtol 1e-3 / atol 1e-2 after BF16/FP16 rounding.
 """
 
 import pytest
@@ -24,6 +27,46 @@ def moe():
     assert _loader.is_available(), "libgrain_b200.so must be built for the GPU tests"
     yield moe
     assert _loader.device_status() == 0, "a kernel reported a bounded-wait timeout"
+
+
+_TABLES = {}
+
+
+def gpu_silu_table(dtype):
+    """The library's SiLU table for `dtype` (BF16/FP16), read back to the host."""
+    if dtype not in _TABLES:
+        from grain_gemm_b200 import _loader
+        table = torch.empty((65536,), dtype=torch.float32, device="cuda")
+        _loader.check(_loader.library().gg_moe_silu_table(
+            _loader.pointer(table), _loader.OUT_DTYPE[dtype], _loader.stream_pointer(table.device)),
+            "gg_moe_silu_table")
+        _TABLES[dtype] = table.cpu()
+    return _TABLES[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_silu_table_against_host_formula(moe, dtype):
+    """Entry by entry: the GPU's silu(v) for every 16-bit pattern against the host's
+    v / (1 + expf(-v)).  CUDA's expf and the host C library's may round differently in the last
+    place; the differing patterns are enumerated here (and printed), each within one unit in
+    the last place, so the set on which the two arithmetics disagree is known, finite and small."""
+    table = gpu_silu_table(dtype)
+    patterns = torch.arange(65536, dtype=torch.int32).to(torch.int16)
+    values = patterns.view(dtype).float()
+    host = oracle.silu(values)
+    finite = torch.isfinite(values)
+    assert torch.equal(torch.isnan(table), torch.isnan(host))
+    same = (table.view(torch.int32) == host.view(torch.int32)) | torch.isnan(host)
+    differing = torch.nonzero(~same).flatten()
+    ulps = (table.view(torch.int32)[differing] - host.view(torch.int32)[differing]).abs()
+    print(f"silu table ({dtype}): {differing.numel()} of 65536 patterns differ from the host "
+          f"formula: {[hex(int(b)) for b in differing[:64]]}{' ...' if differing.numel() > 64 else ''}")
+    assert finite[differing].all()
+    assert differing.numel() < 655            # under 1 % of the patterns
+    assert ulps.numel() == 0 or int(ulps.max()) <= 1
+    # Known answers: silu(0) = 0, silu(+-inf), large |v| saturate to v and -0.
+    zero, one = 0, int(torch.tensor([1.0]).to(dtype).view(torch.int16))
+    assert table[zero] == 0 and table[one] == host[one]
 
 
 def assert_routes_equal(routes, expected):
@@ -131,14 +174,12 @@ def run_stages(moe, case, variant):
     gate_up = oracle.ragged_gemm(case["hidden_states"], case["w_gate_up"].transpose(-2, -1),
                                  case["scale_x"], case["scale_gate_up"], expected_routes, dtype,
                                  source_is_token=True)
-    expected_q, expected_s = oracle.swiglu_quantize(gate_up, valid, layout)
-    q_cpu, s_cpu = qh.cpu()[:valid], sh.cpu()[:valid]
-    torch.testing.assert_close(s_cpu, expected_s[:valid], rtol=2e-6, atol=0)
-    difference = (q_cpu.int() - expected_q[:valid].int()).abs()
-    assert difference.max() <= 1
-    assert (difference != 0).float().mean() < 2e-3
+    expected_q, expected_s = oracle.swiglu_quantize(gate_up, valid, layout,
+                                                    silu_table=gpu_silu_table(dtype))
+    assert torch.equal(sh.cpu()[:valid], expected_s[:valid])
+    assert torch.equal(qh.cpu()[:valid], expected_q[:valid])
 
-    # Down and combine: bit-exact on the CUDA path's own quantised activations.
+    # Down and combine, on the (identical) quantised activations.
     expert_out = moe.down_projection(qh, sh, w2, dev["scale_down"], routes, output_dtype=dtype)
     expected_out = oracle.ragged_gemm(qh.cpu(), case["w_down"].transpose(-2, -1), sh.cpu(),
                                       case["scale_down"], expected_routes, dtype,
@@ -166,6 +207,8 @@ def test_stages_against_oracle(moe, spec, variant):
     staged = run_stages(moe, case, variant)
     full = moe.moe_ffn(**to_cuda(case), variant=variant).cpu()
     assert torch.equal(full, staged)
+    exact = oracle.moe_ffn(**case, silu_table=gpu_silu_table(case["output_dtype"]))
+    assert torch.equal(full, exact)
     expected = oracle.moe_ffn(**{k: v for k, v in case.items()})
     torch.testing.assert_close(full.float(), expected.float(), rtol=RTOL, atol=ATOL)
     if "token_mask" in case:
@@ -252,6 +295,29 @@ def test_fused_gate_up_equals_unfused_bits(moe, layout, dtype):
     assert results[0][0].abs().max() == 127
 
 
+@pytest.mark.parametrize("hidden", [256, 512])
+def test_fused_gate_up_many_items_per_cta_with_short_k(moe, hidden):
+    """H = 256 / 512 gives one or two K groups per sub-tile, so a fast warp reaches the next
+    work item while its partner half still reads the row maxima both exchange through shared
+    memory; with several hundred work items every CTA walks several items back to back.
+    Codes and scales must equal the unfused kernels' bit for bit."""
+    case = make_case(12000, hidden, 512, 6, 2, seed=23)
+    dev = to_cuda(case)
+    w1 = dev["w_gate_up"].transpose(-2, -1)
+    results = []
+    for tile_rows in (128, 32):
+        routes = moe.prepare_routes(dev["topk_ids"], 6, None, tile_rows=tile_rows)
+        if tile_rows == 128:
+            used = int((routes.tile_expert >= 0).sum())
+            assert used * (512 // 256) > 300
+        qh, sh = moe.gate_up_swiglu_quantize(dev["hidden_states"], dev["scale_x"], w1,
+                                             dev["scale_gate_up"], routes)
+        valid = int(routes.offsets[-1])
+        results.append((qh[:valid].cpu(), sh[:valid].cpu()))
+    assert torch.equal(results[0][0], results[1][0])
+    assert torch.equal(results[0][1], results[1][1])
+
+
 def test_interleaved_equals_split_bits(moe):
     split = make_case(200, 512, 512, 6, 2, layout="split", seed=5)
     inter = make_case(200, 512, 512, 6, 2, layout="interleaved", seed=5)
@@ -260,23 +326,62 @@ def test_interleaved_equals_split_bits(moe):
     assert torch.equal(a, b)
 
 
-def test_baseline_config_3_decode_small(moe):
+def check_against_oracle(actual, case):
+    """Bit-exact against the oracle given the GPU's SiLU table, and within the stated
+    tolerance of the oracle that evaluates SiLU with the host's expf."""
+    dtype = case.get("output_dtype", torch.bfloat16)
+    exact = oracle.moe_ffn(**case, silu_table=gpu_silu_table(dtype))
+    assert torch.equal(actual, exact)
+    expected = oracle.moe_ffn(**case)
+    torch.testing.assert_close(actual.float(), expected.float(), rtol=RTOL, atol=ATOL)
+
+
+def test_config_decode_small(moe):
     """T=512, H=2048, I=768, E=128, top-8, split layout, BF16."""
     case = make_case(512, 2048, 768, 128, 8)
-    actual = moe.moe_ffn(**to_cuda(case)).cpu()
-    expected = oracle.moe_ffn(**case)
-    torch.testing.assert_close(actual.float(), expected.float(), rtol=RTOL, atol=ATOL)
+    check_against_oracle(moe.moe_ffn(**to_cuda(case)).cpu(), case)
 
 
-def test_baseline_config_4_interleaved_decode(moe):
+def test_config_interleaved_decode(moe):
     """H=4096, I=14336, E=8, top-2, T=16, one expert biased, interleaved layout."""
     case = make_case(16, 4096, 14336, 8, 2, layout="interleaved", biased=True)
-    actual = moe.moe_ffn(**to_cuda(case)).cpu()
-    expected = oracle.moe_ffn(**case)
-    torch.testing.assert_close(actual.float(), expected.float(), rtol=RTOL, atol=ATOL)
+    check_against_oracle(moe.moe_ffn(**to_cuda(case)).cpu(), case)
 
 
-def test_baseline_config_5_large_sampled_tokens_and_properties(moe):
+def sampled_token_case(case, tokens, experts):
+    """The sub-problem of `tokens` (CPU tensors) on the experts those tokens use."""
+    index = tokens.cuda()
+    ids = case["topk_ids"][index].cpu()
+    used = torch.unique(ids)
+    remap = torch.full((experts,), -1, dtype=torch.int64)
+    remap[used] = torch.arange(used.numel())
+    return dict(
+        hidden_states=case["hidden_states"][index].cpu(),
+        scale_x=case["scale_x"][index].cpu(),
+        topk_weights=case["topk_weights"][index].cpu(),
+        topk_ids=remap[ids],
+        w_gate_up=case["w_gate_up"][used.cuda()].cpu(),
+        w_down=case["w_down"][used.cuda()].cpu(),
+        scale_gate_up=case["scale_gate_up"][used.cuda()].cpu(),
+        scale_down=case["scale_down"][used.cuda()].cpu(),
+        gate_up_layout=case.get("gate_up_layout", "split"))
+
+
+def test_config_interleaved_prefill_sampled_tokens(moe):
+    """H=4096, I=14336, E=8, top-2, T=4096, one expert biased, interleaved layout: sampled
+    tokens against the oracle, bit for bit."""
+    import bench_moe
+
+    case = bench_moe.make_case("interleaved_prefill", torch.device("cuda"))
+    out = moe.moe_ffn(**case)
+    tokens = torch.tensor([0, 1, 255, 2048, 3000, 4095])
+    sub = sampled_token_case(case, tokens, 8)
+    check_against_oracle(out[tokens.cuda()].cpu(), sub)
+    counts = torch.bincount(case["topk_ids"].flatten().cpu(), minlength=8)
+    assert counts[0] > 2 * counts[1:].float().mean()          # the biased expert is loaded more
+
+
+def test_config_large_sampled_tokens_and_properties(moe):
     """T=16384, H=7168, I=2048, E=256, top-8 is far beyond the CPU oracle: check sampled tokens
     against it (on the experts those tokens use) and two size-independent properties:
     doubling every routing weight doubles the output exactly, and zero weights give zero."""
@@ -290,21 +395,8 @@ def test_baseline_config_5_large_sampled_tokens_and_properties(moe):
     assert zeroed.abs().sum() == 0
 
     tokens = torch.tensor([0, 1, 4097, 8191, 12345, 16383])
-    ids = case["topk_ids"][tokens.cuda()].cpu()
-    used = torch.unique(ids)
-    remap = torch.full((256,), -1, dtype=torch.int64)
-    remap[used] = torch.arange(used.numel())
-    sub = dict(
-        hidden_states=case["hidden_states"][tokens.cuda()].cpu(),
-        scale_x=case["scale_x"][tokens.cuda()].cpu(),
-        topk_weights=case["topk_weights"][tokens.cuda()].cpu(),
-        topk_ids=remap[ids],
-        w_gate_up=case["w_gate_up"][used.cuda()].cpu(),
-        w_down=case["w_down"][used.cuda()].cpu(),
-        scale_gate_up=case["scale_gate_up"][used.cuda()].cpu(),
-        scale_down=case["scale_down"][used.cuda()].cpu())
-    expected = oracle.moe_ffn(**sub)
-    torch.testing.assert_close(out[tokens.cuda()].cpu().float(), expected.float(), rtol=RTOL, atol=ATOL)
+    sub = sampled_token_case(case, tokens, 256)
+    check_against_oracle(out[tokens.cuda()].cpu(), sub)
 
 
 def test_graph_replay_with_changed_routes(moe):
