@@ -48,8 +48,8 @@ _SIGNATURES = {
     "gg_moe_topk": (_INT, [_VOID, _INT, _INT, _INT, _INT, _VOID, _VOID, _INT, _VOID]),
     "gg_quantize_rows": (_INT, [_VOID, _INT, _LL, _INT, _INT, _VOID, _VOID, _VOID]),
     "gg_moe_silu_table": (_INT, [_VOID, _INT, _VOID]),
-    "gg_moe_gate_up_scratch_bytes": (_SIZE, [_INT] * 4),
-    "gg_moe_gate_up": (_INT, [_VOID] * 8 + [_INT, _INT] + [_VOID] * 3 + [_INT] * 7 + [_VOID]),
+    "gg_moe_gate_up_scratch_bytes": (_SIZE, [_INT] * 5),
+    "gg_moe_gate_up": (_INT, [_VOID] * 8 + [_INT, _INT] + [_VOID] * 3 + [_INT] * 8 + [_VOID]),
     "gg_moe_down": (_INT, [_VOID] * 7 + [_INT, _INT, _VOID] + [_INT] * 5 + [_VOID]),
     "gg_moe_combine": (_INT, [_VOID] * 4 + [_INT] * 4 + [_VOID]),
     "gg_device_status": (_INT, [ctypes.POINTER(_INT), _VOID]),

@@ -170,11 +170,8 @@ static int launch_tc_kernel(const CUtensorMap& map_a, const CUtensorMap& map_b,
   cudaError_t error =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape::kSmemBytes);
   if (error != cudaSuccess) return static_cast<int>(error);
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
-  const int workers = static_cast<int>(tiles < sm_count() / kCtaGroup ? tiles : sm_count() / kCtaGroup);
-  if (workers <= 0) return 0;
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(workers * kCtaGroup);
+  config.gridDim = dim3(sm_count() / kCtaGroup * kCtaGroup);
   config.blockDim = dim3(Shape::kThreads);
   config.dynamicSmemBytes = Shape::kSmemBytes;
   config.stream = stream;
@@ -185,11 +182,38 @@ static int launch_tc_kernel(const CUtensorMap& map_a, const CUtensorMap& map_b,
   attribute[0].val.clusterDim.z = 1;
   config.attrs = attribute;
   config.numAttrs = 1;
+  // The kernel is persistent: every CTA (pair) of the grid must be resident at once, or the
+  // late ones only start when an early one has finished all of its tiles.  How many pairs fit
+  // depends on the part: a cluster cannot span GPCs, and B200s differ in how their 148 SMs are
+  // spread over GPCs (one with an odd number of SMs strands one SM for pairs).  Immutable per
+  // device and kernel, so asked once.
+  int workers_max = sm_count() / kCtaGroup;
+  if constexpr (kCtaGroup > 1) {
+    static int cached[64] = {0};
+    int device = 0;
+    if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < 64) {
+      if (cached[device] == 0) {
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters <= 0) {
+          clusters = workers_max;
+        }
+        cached[device] = clusters;
+      }
+      if (cached[device] < workers_max) workers_max = cached[device];
+    }
+  }
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const int workers = static_cast<int>(tiles < workers_max ? tiles : workers_max);
+  if (workers <= 0) return 0;
+  config.gridDim = dim3(workers * kCtaGroup);
   error = cudaLaunchKernelEx(&config, kernel, map_a, map_b, p);
   return static_cast<int>(error);
 }
 
-template <int kCtaGroup, int BN, int kStages, bool kGrouped, int kPromoWarps = 8>
+#ifndef GG_PROMO_WARPS
+#define GG_PROMO_WARPS 8
+#endif
+template <int kCtaGroup, int BN, int kStages, bool kGrouped, int kPromoWarps = GG_PROMO_WARPS>
 static int launch_tc_dtype(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmTcParams& p,
                            int out_dtype, cudaStream_t stream) {
   switch (out_dtype) {
@@ -322,17 +346,10 @@ static int run_gemm(const GemmArgs& g, int variant, cudaStream_t stream, void* w
   return launch_gemm_tc(g, variant, stream);
 }
 
-// Row-gather mode of the fused Gate/Up kernel (the shipped mode): the producer fetches token
-// rows from x[T, H] by TMA row gathers and the scratch holds only the SiLU table.  With 0 the
-// rows are first copied into sorted order (kept for measurements).
-#ifndef GG_GATE_UP_GATHER
-#define GG_GATE_UP_GATHER 1
-#endif
-
-template <typename RoundT>
+template <typename RoundT, bool kGather>
 static int launch_gate_up_tc(const CUtensorMap& map_x, const CUtensorMap& map_w,
                              const GateUpParams& p, int grid, cudaStream_t stream) {
-  auto kernel = moe_gate_up_tc_kernel<RoundT, GG_GATE_UP_GATHER != 0>;
+  auto kernel = moe_gate_up_tc_kernel<RoundT, kGather>;
   const cudaError_t error = cudaFuncSetAttribute(
       kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GateUpShape::kSmemBytes);
   if (error != cudaSuccess) return static_cast<int>(error);
@@ -569,11 +586,12 @@ int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, 
   return static_cast<int>(cudaGetLastError());
 }
 
-size_t gg_moe_gate_up_scratch_bytes(int assignments, int hidden, int intermediate, int tile_rows) {
+size_t gg_moe_gate_up_scratch_bytes(int assignments, int hidden, int intermediate, int tile_rows,
+                                    int row_gather) {
   const size_t slots = static_cast<size_t>(assignments > 0 ? assignments : 0);
   if (tile_rows == 128) {
     const size_t table = 65536 * sizeof(float);
-    if (GG_GATE_UP_GATHER) return table;
+    if (row_gather) return table;
     const size_t rows = slots * static_cast<size_t>(hidden > 0 ? hidden : 0);
     const size_t scales = slots * static_cast<size_t>(hidden > 0 ? hidden / 256 : 0) * 4;
     return ((rows + 255) & ~static_cast<size_t>(255)) + ((scales + 255) & ~static_cast<size_t>(255)) +
@@ -595,7 +613,8 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
                    const void* order, const void* offsets, const void* tile_expert,
                    const void* tile_row, int tile_capacity, int tile_rows, void* q, void* s,
                    void* gate_up_scratch, int tokens, int top_k, int experts, int hidden,
-                   int intermediate, int interleaved, int out_dtype, void* stream_ptr) {
+                   int intermediate, int interleaved, int out_dtype, int row_gather,
+                   void* stream_ptr) {
   if (tokens <= 0 || top_k <= 0 || experts <= 0 || hidden <= 0 || intermediate <= 0 ||
       hidden % 256 || intermediate % 256 || tile_capacity <= 0 ||
       (out_dtype != GG_OUT_BF16 && out_dtype != GG_OUT_FP16) || !x || !scale_x || !w1 ||
@@ -613,7 +632,7 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
     gg::GateUpParams p = {};
     CUtensorMap map_x, map_w;
     int status;
-    if (GG_GATE_UP_GATHER) {
+    if (row_gather) {
       p.silu_table = reinterpret_cast<float*>(scratch);
       p.row_scale = static_cast<const float*>(scale_x);
       status = gg::encode_int8_rows(&map_x, x, tokens, hidden, hidden, 1);
@@ -654,8 +673,16 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
     p.max_tiles = tile_capacity; p.interleaved = interleaved;
     const long long items = static_cast<long long>(tile_capacity) * (intermediate / 256);
     const int grid = static_cast<int>(items < gg::sm_count() ? items : gg::sm_count());
-    if (out_dtype == GG_OUT_BF16) return gg::launch_gate_up_tc<__nv_bfloat16>(map_x, map_w, p, grid, stream);
-    return gg::launch_gate_up_tc<__half>(map_x, map_w, p, grid, stream);
+    if (row_gather) {
+      if (out_dtype == GG_OUT_BF16) {
+        return gg::launch_gate_up_tc<__nv_bfloat16, true>(map_x, map_w, p, grid, stream);
+      }
+      return gg::launch_gate_up_tc<__half, true>(map_x, map_w, p, grid, stream);
+    }
+    if (out_dtype == GG_OUT_BF16) {
+      return gg::launch_gate_up_tc<__nv_bfloat16, false>(map_x, map_w, p, grid, stream);
+    }
+    return gg::launch_gate_up_tc<__half, false>(map_x, map_w, p, grid, stream);
   }
   if (tile_rows != gg::kSimtTile || !gate_up_scratch) return static_cast<int>(cudaErrorInvalidValue);
   // CUDA-core path: ragged gathered GEMM into the scratch matrix, then SwiGLU + requantisation.

@@ -35,15 +35,6 @@
 
 namespace gg {
 
-// Build switches (both on in the shipped library; the off positions are kept for measurements).
-//  GG_TMEM_BIAS      accumulators preset to kAccumulatorBias, float(dot) by one FP32 subtraction
-//  GG_SCALE_PERMUTE  scale ring stored in the order the promotion threads read it (16-byte loads)
-#ifndef GG_TMEM_BIAS
-#define GG_TMEM_BIAS 1
-#endif
-#ifndef GG_SCALE_PERMUTE
-#define GG_SCALE_PERMUTE 1
-#endif
 // Register split between the eight promotion warps and the four auxiliary warps (setmaxnreg).
 #ifndef GG_PROMO_REGS
 #define GG_PROMO_REGS 216
@@ -51,8 +42,14 @@ namespace gg {
 #ifndef GG_AUX_REGS
 #define GG_AUX_REGS 64
 #endif
-constexpr bool kTmemBias = GG_TMEM_BIAS != 0;
-constexpr bool kScalePermute = GG_SCALE_PERMUTE != 0;
+// TMEM drain layout of the GEMM kernel (see FragmentLayout); 0 keeps the pairs layout for
+// measurements.
+#ifndef GG_EXP
+#define GG_EXP 0
+#endif
+#ifndef GG_GEMM_FRAGMENT_QUADS
+#define GG_GEMM_FRAGMENT_QUADS 1
+#endif
 
 struct GemmTcParams {
   const float* scale_a;
@@ -102,7 +99,9 @@ struct GemmTcShape {
   static constexpr int kBBytes = kBRows * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemColumns = 2 * BN;
-  static constexpr int kScaleSlots = 4;                 // ring of per-group scale vectors
+  // Ring of per-group scale vectors (the short-A shape is the split-K dump kernel, which
+  // stages no scales and needs the room for its operand stages).
+  static constexpr int kScaleSlots = kARows == 128 ? 8 : 4;
   static constexpr int kScaleSlotFloats = BN + 128;     // scale_b columns, then scale_a rows
   static constexpr int kScaleBytes = kScaleSlots * kScaleSlotFloats * 4;
   static constexpr int kBarrierBytes = (2 * kStages + 4 + 2 * kScaleSlots) * 8 + 16;
@@ -158,73 +157,74 @@ __device__ __forceinline__ TileWork decode_tile(const GemmTcParams& p, int tile)
   return w;
 }
 
-// Position of accumulator column `c` (0..31 within its 32-column block) in the scale ring:
-// the thread with quad index q = lane % 4 reads the eight scales of its columns
-// 8i + 2q, 8i + 2q + 1 (i = 0..3) as two 16-byte vectors at q * 8.
+// TMEM drain layouts.  A promotion warp reads its 32 lanes x 32 columns of a block as two
+// fragments of 16 lanes; with r = lane / 4 and q = lane % 4 a thread receives rows r, r + 8
+// (and r + 16, r + 24 from the second fragment) and eight columns of the block:
+//   kFragmentPairs (tcgen05.ld.16x256b.x4): the pairs 8j + 2q, 8j + 2q + 1   (j = 0..3)
+//   kFragmentQuads (tcgen05.ld.16x128b.x8): the columns 4k + q               (k = 0..7)
+// Both need the same scales per thread (4 row scales, 8 column scales per block), far fewer
+// than the row-per-thread 32x32b shape, whose broadcast scale loads saturate the shared-memory
+// return path.  Measured on B200 with eight warps draining 128 lanes x 256 columns: 16x256b
+// delivers 256 B/clk/SM, 16x128b 507 B/clk/SM (32x32b 940 B/clk/SM), so the quad layout halves
+// the time the drain keeps TMEM's read port busy.
+enum FragmentLayout { kFragmentPairs = 0, kFragmentQuads = 1 };
+
+// The accumulator pair j (j = 0..3) of a thread holds the block's columns
+//   pairs layout: 8j + 2q, 8j + 2q + 1        quads layout: 8j + q, 8j + 4 + q.
+// Position of block column `c` (0..31) in the scale ring: thread q reads its eight column
+// scales, in accumulator-pair order, as two 16-byte vectors at q * 8.
+template <FragmentLayout kLayout>
 __device__ __forceinline__ int ring_column_position(int c) {
-  return kScalePermute ? ((c >> 1) & 3) * 8 + (c >> 3) * 2 + (c & 1) : c;
+  if constexpr (kLayout == kFragmentPairs) return ((c >> 1) & 3) * 8 + (c >> 3) * 2 + (c & 1);
+  else return (c & 3) * 8 + (c >> 3) * 2 + ((c >> 2) & 1);
 }
 // Position of row `r` (0..31 within its warp's 32 rows): the thread with row index
 // lane / 4 = r % 8 reads its four rows r % 8 + 8j as one 16-byte vector.
-__device__ __forceinline__ int ring_row_position(int r) {
-  return kScalePermute ? (r & 7) * 4 + (r >> 3) : r;
-}
+__device__ __forceinline__ int ring_row_position(int r) { return (r & 7) * 4 + (r >> 3); }
 
 // The eight column scales (four pairs) of this thread for one 32-column block.
 __device__ __forceinline__ void load_column_scales(const float* block_base, int quad,
                                                    float2 (&sb)[4]) {
-  if constexpr (kScalePermute) {
-    const float4 lo = *reinterpret_cast<const float4*>(block_base + quad * 8);
-    const float4 hi = *reinterpret_cast<const float4*>(block_base + quad * 8 + 4);
-    sb[0] = make_float2(lo.x, lo.y);
-    sb[1] = make_float2(lo.z, lo.w);
-    sb[2] = make_float2(hi.x, hi.y);
-    sb[3] = make_float2(hi.z, hi.w);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      sb[i] = *reinterpret_cast<const float2*>(block_base + 8 * i + 2 * quad);
-  }
+  const float4 lo = *reinterpret_cast<const float4*>(block_base + quad * 8);
+  const float4 hi = *reinterpret_cast<const float4*>(block_base + quad * 8 + 4);
+  sb[0] = make_float2(lo.x, lo.y);
+  sb[1] = make_float2(lo.z, lo.w);
+  sb[2] = make_float2(hi.x, hi.y);
+  sb[3] = make_float2(hi.z, hi.w);
 }
 // The four row scales of this thread (rows fragment_row + 8j of the warp's 32 rows).
 __device__ __forceinline__ void load_row_scales(const float* warp_rows_base, int fragment_row,
                                                 float (&sa)[4]) {
-  if constexpr (kScalePermute) {
-    const float4 v = *reinterpret_cast<const float4*>(warp_rows_base + fragment_row * 4);
-    sa[0] = v.x; sa[1] = v.y; sa[2] = v.z; sa[3] = v.w;
-  } else {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) sa[j] = warp_rows_base[fragment_row + 8 * j];
-  }
+  const float4 v = *reinterpret_cast<const float4*>(warp_rows_base + fragment_row * 4);
+  sa[0] = v.x; sa[1] = v.y; sa[2] = v.z; sa[3] = v.w;
 }
 
-// Promotion of one 16-row x 32-column fragment (tmem_ld_16x256b_x4 layout): this thread holds
-// rows r and r+8 and column pairs 8i+2q, 8i+2q+1.  `sb` are its four column-scale pairs, read
-// once per 32-column block and used for both 16-row halves.  kBiased: the words are
-// kAccumulatorBias + dot (see ptx.cuh) and float(dot) is an exact packed subtraction.
-template <bool kBiased>
+template <FragmentLayout kLayout>
+__device__ __forceinline__ void tmem_ld_fragment(uint32_t taddr, uint32_t (&r)[16]) {
+  if constexpr (kLayout == kFragmentPairs) tmem_ld_16x256b_x4(taddr, r);
+  else tmem_ld_16x128b_x8(taddr, r);
+}
+
+// Promotion of one 16-row x 32-column fragment: this thread holds rows r ("low") and r + 8
+// ("high") and four column pairs; `sb` are the scales of those pairs, read once per 32-column
+// block and used for both 16-row fragments.  Registers: pairs layout 4j + {0,1} = low pair j,
+// 4j + {2,3} = high pair j; quads layout 4j + {0,2} = low pair j, 4j + {1,3} = high pair j.
+template <FragmentLayout kLayout>
 __device__ __forceinline__ void promote_fragment(const uint32_t (&partial)[16], float sa_low,
                                                  float sa_high, const float2 (&sb)[4],
                                                  float2* acc_low, float2* acc_high) {
+  constexpr int kLowY = kLayout == kFragmentPairs ? 1 : 2;
+  constexpr int kHighX = kLayout == kFragmentPairs ? 2 : 1;
   const float2 sa_low2 = make_float2(sa_low, sa_low);
   const float2 sa_high2 = make_float2(sa_high, sa_high);
-  const float2 minus_bias = make_float2(-kAccumulatorBiasValue, -kAccumulatorBiasValue);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 low, high;
-    if constexpr (kBiased) {
-      low = __fadd2_rn(make_float2(__uint_as_float(partial[4 * i + 0]),
-                                   __uint_as_float(partial[4 * i + 1])), minus_bias);
-      high = __fadd2_rn(make_float2(__uint_as_float(partial[4 * i + 2]),
-                                    __uint_as_float(partial[4 * i + 3])), minus_bias);
-    } else {
-      low = make_float2(__int2float_rn(static_cast<int>(partial[4 * i + 0])),
-                        __int2float_rn(static_cast<int>(partial[4 * i + 1])));
-      high = make_float2(__int2float_rn(static_cast<int>(partial[4 * i + 2])),
-                         __int2float_rn(static_cast<int>(partial[4 * i + 3])));
-    }
-    acc_low[i] = __ffma2_rn(low, __fmul2_rn(sa_low2, sb[i]), acc_low[i]);
-    acc_high[i] = __ffma2_rn(high, __fmul2_rn(sa_high2, sb[i]), acc_high[i]);
+  for (int j = 0; j < 4; ++j) {
+    const float2 low = make_float2(__int2float_rn(static_cast<int>(partial[4 * j + 0])),
+                                   __int2float_rn(static_cast<int>(partial[4 * j + kLowY])));
+    const float2 high = make_float2(__int2float_rn(static_cast<int>(partial[4 * j + kHighX])),
+                                    __int2float_rn(static_cast<int>(partial[4 * j + 3])));
+    acc_low[j] = __ffma2_rn(low, __fmul2_rn(sa_low2, sb[j]), acc_low[j]);
+    acc_high[j] = __ffma2_rn(high, __fmul2_rn(sa_high2, sb[j]), acc_high[j]);
   }
 }
 
@@ -266,6 +266,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr int kNC = Shape::kColumnsPerThread;   // columns owned by one promotion thread
   constexpr int kProducerWarp = kPromoWarps, kMmaWarp = kPromoWarps + 1;
   constexpr int kScaleWarp = kPromoWarps + 2;
+  constexpr FragmentLayout kLayout = GG_GEMM_FRAGMENT_QUADS ? kFragmentQuads : kFragmentPairs;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -317,32 +318,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if constexpr (kCtaGroup == 2) cluster_sync_all();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  constexpr bool kBias = kTmemBias && !kDump;
-
-  if constexpr (kBias) {
-    // Every accumulator word starts at the bias: each promotion warp presets the lanes and
-    // columns it will later drain, in both buffers, before the first MMA may be issued.
-    if (warp < kPromoWarps) {
-      uint32_t bias[16];
-      make_bias_block(bias);
-      const uint32_t lanes = static_cast<uint32_t>((warp & 3) * 32) << 16;
-#pragma unroll
-      for (int buffer = 0; buffer < 2; ++buffer) {
-#pragma unroll
-        for (int block = 0; block < kNC / 32; ++block) {
-          const uint32_t taddr = tmem_base + lanes + buffer * BN + (warp >> 2) * kNC + block * 32;
-          tmem_st_16x256b_x4(taddr, bias);
-          tmem_st_16x256b_x4(taddr + (16u << 16), bias);
-        }
-      }
-      tmem_st_wait();
-    }
-    tcgen05_fence_before();
-    __syncthreads();
-    if constexpr (kCtaGroup == 2) cluster_sync_all();
-    tcgen05_fence_after();
-  }
-
   // The last four warps (producer, MMA issuer, two spares) give registers to the promotion warps.
   if (warp >= kPromoWarps) {
   setmaxnreg_dec<Shape::kAuxRegisters>();
@@ -374,7 +349,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (leader) {
           uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
           uint8_t* b_dst = a_dst + Shape::kABytes;
-          if constexpr (kCtaGroup == 1) {
+          if constexpr ((GG_EXP & 8) != 0) {
+            if (cta_rank == 0) mbar_arrive(&full_bar[stage]);
+          } else if constexpr (kCtaGroup == 1) {
             mbar_expect_tx(&full_bar[stage], Shape::kStageBytes);
             tma_load_2d(a_dst, &map_a, &full_bar[stage], x, row_a);
             tma_load_2d(b_dst, &map_b, &full_bar[stage], x, row_b);
@@ -429,7 +406,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t b_low = a_low + (Shape::kABytes >> 4);
             const uint32_t tmem_d = tmem_base + buffer * BN;
             if (leader) {
-              umma_i8<kCtaGroup>(tmem_d, a_low, b_low, idesc, (kBias || !group_start) ? 1u : 0u);
+              umma_i8<kCtaGroup>(tmem_d, a_low, b_low, idesc, group_start ? 0u : 1u);
               umma_i8<kCtaGroup>(tmem_d, a_low + 2, b_low + 2, idesc, 1u);
               umma_i8<kCtaGroup>(tmem_d, a_low + 4, b_low + 4, idesc, 1u);
               umma_i8<kCtaGroup>(tmem_d, a_low + 6, b_low + 6, idesc, 1u);
@@ -473,7 +450,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               }
               if (leader) {
                 umma_i8<kCtaGroup>(tmem_base + buffer * BN, a_low + 2 * j, b_low + 2 * j, idesc,
-                                   (kBias || step != 0) ? 1u : 0u);
+                                   step != 0 ? 1u : 0u);
               }
               ++step;
               --remaining;
@@ -499,10 +476,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
-  } else if (warp == kScaleWarp && !kDump) {
+  } else if (warp == kScaleWarp && !kDump && (GG_EXP & 4) == 0) {
     // ------------------------------------------------------------ scale staging warp
-    // Copies each group's scale_b columns and scale_a rows into a shared-memory ring, one
-    // group ahead in registers, so that the promotion warps never wait on global memory.
+    // Copies each group's scale_b columns and scale_a rows into a shared-memory ring with
+    // asynchronous 4-byte copies (cp.async) that land directly in the order the promotion
+    // threads read; each lane's copies signal the slot's barrier when they have arrived.
+    // Nothing passes through registers, so the warp runs a whole ring ahead of the promotion
+    // warps and a global-memory latency of several K groups stays hidden (a version that
+    // held one group in registers left the promotion warps waiting for scales).
     constexpr int kColumnsPerLane = BN / 32;
     uint32_t slot = 0, phase = 0;
     bool ok = true;
@@ -521,46 +502,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         row_limit = p.m;
       }
       const int n0 = work.tn * BN;
-      float sb_next[kColumnsPerLane], sa_next[4];
-      auto fetch = [&](int g) {
+      // Per-lane sources and destinations do not change within the tile.
+      const float* sb_source[kColumnsPerLane];
+      const float* sa_source[4];
+      bool sb_valid[kColumnsPerLane], sa_valid[4];
 #pragma unroll
-        for (int i = 0; i < kColumnsPerLane; ++i) {
-          const int col = n0 + lane + 32 * i;
-          sb_next[i] = col < p.n ? sb_base[g * p.sb_sg + col * p.sb_sn] : 0.0f;
-        }
+      for (int i = 0; i < kColumnsPerLane; ++i) {
+        const int col = n0 + lane + 32 * i;
+        sb_valid[i] = col < p.n;
+        sb_source[i] = sb_base + (sb_valid[i] ? col * p.sb_sn : 0);
+      }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = row0 + lane + 32 * i;
-          sa_next[i] = r < row_limit ? p.scale_a[r * p.sa_sm + g * p.sa_sg] : 0.0f;
-        }
-      };
-      fetch(work.group_begin);
+      for (int i = 0; i < 4; ++i) {
+        const int r = row0 + lane + 32 * i;
+        sa_valid[i] = r < row_limit;
+        sa_source[i] = p.scale_a + (sa_valid[i] ? r * p.sa_sm : 0);
+      }
+      const int column_position = ring_column_position<kLayout>(lane);
+      const int row_position = ring_row_position(lane);
       for (int g = 0; g < work.groups; ++g) {
-        float sb_now[kColumnsPerLane], sa_now[4];
-#pragma unroll
-        for (int i = 0; i < kColumnsPerLane; ++i) sb_now[i] = sb_next[i];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sa_now[i] = sa_next[i];
-        if (g + 1 < work.groups) fetch(work.group_begin + g + 1);
         const bool got = mbar_test(&scale_empty_bar[slot], phase ^ 1u) ||
                          mbar_wait(&scale_empty_bar[slot], phase ^ 1u, kSiteScaleEmpty, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
           ok = false;
           break;
         }
+        const long long group = work.group_begin + g;
         float* destination = scale_ring + slot * Shape::kScaleSlotFloats;
 #pragma unroll
-        for (int i = 0; i < kColumnsPerLane; ++i)
-          destination[32 * i + ring_column_position(lane)] = sb_now[i];
+        for (int i = 0; i < kColumnsPerLane; ++i) {
+          cp_async_f32(destination + 32 * i + column_position, sb_source[i] + group * p.sb_sg,
+                       sb_valid[i]);
+        }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) destination[BN + 32 * i + ring_row_position(lane)] = sa_now[i];
-        mbar_arrive(&scale_full_bar[slot]);
+        for (int i = 0; i < 4; ++i) {
+          cp_async_f32(destination + BN + 32 * i + row_position, sa_source[i] + group * p.sa_sg,
+                       sa_valid[i]);
+        }
+        cp_async_arrive(&scale_full_bar[slot]);
         if (++slot == Shape::kScaleSlots) {
           slot = 0;
           phase ^= 1u;
         }
       }
     }
+    cp_async_wait_all();
   }
   } else {
     setmaxnreg_inc<Shape::kPromoRegisters>();
@@ -651,19 +637,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       static_assert(!kDump || kCtaGroup == 1, "split-K dump runs on single CTAs");
       const int fragment_row = lane >> 2;
 
-      [[maybe_unused]] uint32_t bias[16];
-      if constexpr (kBias) make_bias_block(bias);
-
       // `ok` is the same in every lane (mbar_wait_warp votes), so the .sync.aligned TMEM
       // instructions below always see a converged warp, also after a wait has run out.
       for (int g = 0; g < groups; ++g, ++group_sequence) {
         // This group's scales, staged by the scale warp.
-        if (ok) {
+        if (ok && (GG_EXP & 4) == 0) {
           ok = mbar_wait_warp(&scale_full_bar[scale_slot], scale_phase, kSiteScaleFull, abort_flag);
         }
         const float* scale_slot_base = scale_ring + scale_slot * Shape::kScaleSlotFloats;
-        float sa[4];
-        load_row_scales(scale_slot_base + BN + quarter * 32, fragment_row, sa);
+        float sa[4] = {1.f, 1.f, 1.f, 1.f};
+        if ((GG_EXP & 4) == 0) load_row_scales(scale_slot_base + BN + quarter * 32, fragment_row, sa);
         const uint32_t buffer = group_sequence & 1u;
         if (ok) {
           ok = mbar_wait_warp(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
@@ -675,29 +658,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * BN + col_base;
         const uint32_t taddr_high = taddr_low + (16u << 16);
         // Fragments alternate between the two 16-row halves of each 32-column block; the load
-        // of the next fragment is in flight while the current one is promoted.  With biased
-        // accumulators every fragment is reset to the bias as soon as it has been read.
+        // of the next fragment is in flight while the current one is promoted.
         uint32_t partial_a[16], partial_b[16];
         float2 sb[4];
         if (ok) {
-          tmem_ld_16x256b_x4(taddr_low, partial_a);
+          if ((GG_EXP & 2) == 0) tmem_ld_fragment<kLayout>(taddr_low, partial_a);
 #pragma unroll
           for (int fragment = 0; fragment < 2 * kBlocks; ++fragment) {
             const int block = fragment >> 1;
             const int high_half = fragment & 1;
-            if (!high_half) load_column_scales(sb_columns + block * 32, lane & 3, sb);
-            tmem_ld_wait();
-            if constexpr (kBias) {
-              tmem_st_16x256b_x4((high_half ? taddr_high : taddr_low) + block * 32, bias);
-            }
+            if (!high_half && (GG_EXP & 4) == 0) load_column_scales(sb_columns + block * 32, lane & 3, sb);
+            if ((GG_EXP & 2) == 0) tmem_ld_wait();
             if (fragment + 1 < 2 * kBlocks) {
               const uint32_t next = ((fragment + 1) & 1 ? taddr_high : taddr_low) +
                                     ((fragment + 1) >> 1) * 32;
-              if (fragment & 1) tmem_ld_16x256b_x4(next, partial_a);
-              else tmem_ld_16x256b_x4(next, partial_b);
+              if ((GG_EXP & 2) != 0) {}
+              else if (fragment & 1) tmem_ld_fragment<kLayout>(next, partial_a);
+              else tmem_ld_fragment<kLayout>(next, partial_b);
             } else {
               // All of this warp's TMEM accesses for the buffer are done: hand it back.
-              if constexpr (kBias) tmem_st_wait();
               tcgen05_fence_before();
               __syncwarp();
               if (lane == 0) {
@@ -705,27 +684,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 else mbar_arrive_cluster(&tmem_empty_bar[buffer], 0);
               }
             }
-            if (fragment & 1) {
-              promote_fragment<kBias>(partial_b, sa[2], sa[3], sb, &acc[2][block * 4],
+            if ((GG_EXP & 1) != 0) {
+            } else if (fragment & 1) {
+              promote_fragment<kLayout>(partial_b, sa[2], sa[3], sb, &acc[2][block * 4],
                                       &acc[3][block * 4]);
             } else {
-              promote_fragment<kBias>(partial_a, sa[0], sa[1], sb, &acc[0][block * 4],
+              promote_fragment<kLayout>(partial_a, sa[0], sa[1], sb, &acc[0][block * 4],
                                       &acc[1][block * 4]);
             }
           }
         }
         // Every lane has consumed the slot's values (they fed the arithmetic above).
         __syncwarp();
-        if (lane == 0) mbar_arrive(&scale_empty_bar[scale_slot]);
+        if (lane == 0 && (GG_EXP & 4) == 0) mbar_arrive(&scale_empty_bar[scale_slot]);
         if (++scale_slot == Shape::kScaleSlots) {
           scale_slot = 0;
           scale_phase ^= 1u;
         }
       }
-      // The fragment layout leaves each lane with column pairs 8 apart.  A 4x4 exchange inside
-      // every quad gives lane q the eight consecutive columns 8q..8q+7 of each 32-column
-      // block, so that a row leaves as 16-byte stores (a quarter of the store instructions and
-      // of the memory-pipe wavefronts of pair stores).
+      // The fragment layout leaves each lane with columns spread over the block.  A 4x4
+      // exchange inside every quad gives lane q the eight consecutive columns 8q..8q+7 of each
+      // 32-column block (after it, accumulator pair i of the quads layout holds columns
+      // 8q + i and 8q + 4 + i), so that a row leaves as 16-byte stores: a quarter of the store
+      // instructions and of the memory-pipe wavefronts of pair stores.
       if (ok) {
         const int quad = lane & 3;
         const int first_row = row - row_in_cta + quarter * 32 + fragment_row;
@@ -743,6 +724,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
               for (int i = 0; i < 4; ++i) w[i] = pack_pair<OutT>(acc[r][block * 4 + i]);
               quad_transpose(w, quad);
+              if constexpr (kLayout == kFragmentQuads) {
+                const uint32_t v0 = w[0], v1 = w[1], v2 = w[2], v3 = w[3];
+                w[0] = __byte_perm(v0, v1, 0x5410);
+                w[1] = __byte_perm(v2, v3, 0x5410);
+                w[2] = __byte_perm(v0, v1, 0x7632);
+                w[3] = __byte_perm(v2, v3, 0x7632);
+              }
               if (row_stored) {
                 if (aligned && col + 8 <= p.n) {
                   *reinterpret_cast<uint4*>(c_row + col) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -767,14 +755,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               if (row_stored) {
                 if (aligned && col + 8 <= p.n) {
                   uint4* out = reinterpret_cast<uint4*>(c_row + col);
-                  out[0] = make_uint4(wx[0], wy[0], wx[1], wy[1]);
-                  out[1] = make_uint4(wx[2], wy[2], wx[3], wy[3]);
+                  if constexpr (kLayout == kFragmentQuads) {
+                    out[0] = make_uint4(wx[0], wx[1], wx[2], wx[3]);
+                    out[1] = make_uint4(wy[0], wy[1], wy[2], wy[3]);
+                  } else {
+                    out[0] = make_uint4(wx[0], wy[0], wx[1], wy[1]);
+                    out[1] = make_uint4(wx[2], wy[2], wx[3], wy[3]);
+                  }
                 } else {
                   uint32_t* out = reinterpret_cast<uint32_t*>(c_row);
+                  constexpr int kStepX = kLayout == kFragmentQuads ? 1 : 2;
+                  constexpr int kOffsetY = kLayout == kFragmentQuads ? 4 : 1;
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
-                    if (col + 2 * j < p.n) out[col + 2 * j] = wx[j];
-                    if (col + 2 * j + 1 < p.n) out[col + 2 * j + 1] = wy[j];
+                    if (col + kStepX * j < p.n) out[col + kStepX * j] = wx[j];
+                    if (col + kStepX * j + kOffsetY < p.n) out[col + kStepX * j + kOffsetY] = wy[j];
                   }
                 }
               }

@@ -53,7 +53,7 @@ struct GateUpShape {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStashBytes = 256 * 64 * 4;   // 64 parked FP32 values per promotion thread
   static constexpr int kRingFloats = 256 + 128;   // column scales then row scales of one group
-  static constexpr int kScaleSlots = 4;
+  static constexpr int kScaleSlots = 8;
   static constexpr int kScaleBytes = kScaleSlots * kRingFloats * 4;
   static constexpr int kAmaxBytes = 2 * 4 * 128 * 4;   // two item parities x (sub, half) x 128 rows
   static constexpr int kBarrierBytes = (2 * kStages + 4 + 2 * kScaleSlots) * 8 + 16;
@@ -156,27 +156,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  constexpr bool kBias = kTmemBias;
-
-  if constexpr (kBias) {
-    // Every accumulator word starts at the bias (see kAccumulatorBias): each promotion warp
-    // presets its 32 lanes of all 512 columns before the first MMA may be issued.
-    if (warp < 8) {
-      uint32_t bias[16];
-      make_bias_block(bias);
-      const uint32_t lanes = static_cast<uint32_t>((warp & 3) * 32) << 16;
-#pragma unroll
-      for (int block = 0; block < 8; ++block) {
-        const uint32_t taddr = tmem_base + lanes + (warp >> 2) * 256 + block * 32;
-        tmem_st_16x256b_x4(taddr, bias);
-        tmem_st_16x256b_x4(taddr + (16u << 16), bias);
-      }
-      tmem_st_wait();
-    }
-    tcgen05_fence_before();
-    __syncthreads();
-    tcgen05_fence_after();
-  }
+  constexpr FragmentLayout kLayout = kFragmentPairs;
 
   // Warps 8-11 (producer, MMA issuer, two spares) give registers to the promotion warps.
   if (warp >= 8) {
@@ -232,40 +212,38 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     } else if (warp == 10) {
       // ---------------------------------------------------------- scale staging warp
       // Copies each group's 256 column scales (by accumulator column) and 128 row scales into a
-      // shared-memory ring, one group ahead in registers, so that the promotion warps neither
-      // wait on global memory nor on each other.
+      // shared-memory ring with asynchronous 4-byte copies that land in the order the
+      // promotion threads read; the copies themselves signal the slot's barrier, so the warp
+      // runs a whole ring ahead and global-memory latency stays hidden.
       uint32_t slot = 0, phase = 0;
       bool ok = true;
+      const int column_position = ring_column_position<kLayout>(lane);
+      const int row_position = ring_row_position(lane);
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         int tile, jg, expert;
         if (!gate_up_item(p, item, channel_groups, tile, jg, expert)) continue;
         const int row0 = p.tile_row[tile];
         const int row_end = p.expert_offsets[expert + 1];
         const float* sb_base = p.scale_w + static_cast<long long>(expert) * groups * 2 * p.intermediate;
-        long long scale_row[4];   // row of row_scale for tile rows lane + 32 * i
+        const float* sa_source[4];   // row of row_scale for tile rows lane + 32 * i
+        bool sa_valid[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int r = row0 + lane + 32 * i;
-          scale_row[i] = kGather ? gate_up_source_row(p, r, row_end) : r;
+          sa_valid[i] = r < row_end;
+          const long long source_row = kGather ? gate_up_source_row(p, r, row_end) : (sa_valid[i] ? r : 0);
+          sa_source[i] = p.row_scale + source_row * groups;
         }
         for (int sub = 0; sub < 2 && ok; ++sub) {
           const int channel0 = jg * 256 + sub * 128;
-          float sb_next[8], sa_next[4];
-          auto fetch = [&](int g) {
+          const float* sb_source[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int c = lane + 32 * i;   // accumulator column
-              const int sb_col = p.interleaved ? 2 * channel0 + c
-                                               : (i < 4 ? channel0 + c : p.intermediate + channel0 + c - 128);
-              sb_next[i] = sb_base[static_cast<long long>(g) * 2 * p.intermediate + sb_col];
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int r = row0 + lane + 32 * i;
-              sa_next[i] = r < row_end ? p.row_scale[scale_row[i] * groups + g] : 0.0f;
-            }
-          };
-          fetch(0);
+          for (int i = 0; i < 8; ++i) {
+            const int c = lane + 32 * i;   // accumulator column
+            const int sb_col = p.interleaved ? 2 * channel0 + c
+                                             : (i < 4 ? channel0 + c : p.intermediate + channel0 + c - 128);
+            sb_source[i] = sb_base + sb_col;
+          }
           for (int g = 0; g < groups; ++g) {
             const bool got = mbar_test(&scale_empty_bar[slot], phase ^ 1u) ||
                              mbar_wait(&scale_empty_bar[slot], phase ^ 1u, kSiteScaleEmpty, abort_flag);
@@ -275,18 +253,23 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             }
             float* destination = sb_ring + slot * Shape::kRingFloats;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) destination[32 * i + ring_column_position(lane)] = sb_next[i];
+            for (int i = 0; i < 8; ++i) {
+              cp_async_f32(destination + 32 * i + column_position,
+                           sb_source[i] + static_cast<long long>(g) * 2 * p.intermediate, true);
+            }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) destination[BN + 32 * i + ring_row_position(lane)] = sa_next[i];
-            mbar_arrive(&scale_full_bar[slot]);
+            for (int i = 0; i < 4; ++i) {
+              cp_async_f32(destination + BN + 32 * i + row_position, sa_source[i] + g, sa_valid[i]);
+            }
+            cp_async_arrive(&scale_full_bar[slot]);
             if (++slot == Shape::kScaleSlots) {
               slot = 0;
               phase ^= 1u;
             }
-            if (g + 1 < groups) fetch(g + 1);
           }
         }
       }
+      cp_async_wait_all();
     }
   } else {
     // ------------------------------------------------------------ MMA issuer
@@ -321,7 +304,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             const uint32_t b_low = a_low + (Shape::kABytes >> 4);
             const uint32_t tmem_d = tmem_base + buffer * BN;
             if (leader) {
-              umma_i8<1>(tmem_d, a_low, b_low, idesc, (kBias || !group_start) ? 1u : 0u);
+              umma_i8<1>(tmem_d, a_low, b_low, idesc, group_start ? 0u : 1u);
               umma_i8<1>(tmem_d, a_low + 2, b_low + 2, idesc, 1u);
               umma_i8<1>(tmem_d, a_low + 4, b_low + 4, idesc, 1u);
               umma_i8<1>(tmem_d, a_low + 6, b_low + 6, idesc, 1u);
@@ -359,8 +342,6 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     uint32_t scale_slot = 0, scale_phase = 0;
     bool ok = true;
     float4* stash4 = reinterpret_cast<float4*>(stash) + tid;   // element j at stash4[j * 256]
-    [[maybe_unused]] uint32_t bias[16];
-    if constexpr (kBias) make_bias_block(bias);
     // The row-maximum exchange buffer alternates between two copies from one work item to the
     // next: a warp may start the next item (and write its sub-tile 0 maxima) while its partner
     // half is still reading this item's; the barrier of the next item keeps it from getting
@@ -415,10 +396,6 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
               const int block = fragment >> 1;
               if ((fragment & 1) == 0) load_column_scales(slot + block_column[block], quad, sb);
               tmem_ld_wait();
-              if constexpr (kBias) {
-                tmem_st_16x256b_x4(((fragment & 1) ? taddr_high : taddr_low) + block_column[block],
-                                   bias);
-              }
               if (fragment + 1 < 8) {
                 const uint32_t next = ((fragment + 1) & 1 ? taddr_high : taddr_low) +
                                       block_column[(fragment + 1) >> 1];
@@ -426,16 +403,15 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                 else tmem_ld_16x256b_x4(next, partial_b);
               } else {
                 // All of this warp's TMEM accesses for the buffer are done: hand it back.
-                if constexpr (kBias) tmem_st_wait();
                 tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tmem_empty_bar[buffer]);
               }
               if (fragment & 1) {
-                promote_fragment<kBias>(partial_b, sa[2], sa[3], sb, &acc[2][block * 4],
+                promote_fragment<kLayout>(partial_b, sa[2], sa[3], sb, &acc[2][block * 4],
                                         &acc[3][block * 4]);
               } else {
-                promote_fragment<kBias>(partial_a, sa[0], sa[1], sb, &acc[0][block * 4],
+                promote_fragment<kLayout>(partial_a, sa[0], sa[1], sb, &acc[0][block * 4],
                                         &acc[1][block * 4]);
               }
             }

@@ -84,7 +84,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta)
       "{\n\t"
       ".reg .b32 remote;\n\t"
       "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t"
+      "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t"
       "}" ::"r"(smem_u32(bar)), "r"(cta)
       : "memory");
 }
@@ -166,6 +166,25 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, u
                                                uint64_t limit_ns = kWaitLimitNs) {
   const bool got = mbar_test(bar, parity) || mbar_wait(bar, parity, site, abort_flag, limit_ns);
   return __all_sync(0xffffffffu, got);
+}
+
+// ---------------------------------------------------------------- cp.async (scale staging)
+
+// Asynchronous 4-byte copy global -> shared; `valid == false` writes zero without reading.
+__device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* src, bool valid) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(smem_dst)), "l"(src),
+               "r"(valid ? 4 : 0)
+               : "memory");
+}
+
+// One arrival on `bar` once all cp.async issued so far by this thread have landed (the
+// arrival is already part of the barrier's expected count).
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- TMA
@@ -350,34 +369,18 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Store counterpart of tmem_ld_16x256b_x4 (same element-to-register mapping).
-__device__ __forceinline__ void tmem_st_16x256b_x4(uint32_t taddr, const uint32_t (&r)[16]) {
+// 16 TMEM lanes x 32 columns as 4-column groups: with q = lane % 4 and r = lane / 4, register
+// 2k holds row r, column 4k + q and register 2k + 1 holds row r + 8, same column (k = 0..7).
+// Drains TMEM at twice the rate of the 16x256b shape (507 against 256 B/clk/SM measured).
+__device__ __forceinline__ void tmem_ld_16x128b_x8(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
-      "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      "tcgen05.ld.sync.aligned.16x128b.x8.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
       : "memory");
-}
-
-__device__ __forceinline__ void tmem_st_wait() {
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
-// Accumulator bias.  A K group's INT32 dot p satisfies |p| <= 2^22 (256 * 128 * 128), so the
-// integer 0x4B400000 + p, read as FP32, is exactly 12582912 + p (1.5 * 2^23 has unit spacing
-// up to 2^24).  The promotion warps therefore keep every accumulator word of TMEM preset to
-// kAccumulatorBias, the tensor core always accumulates onto it, and float(p) is one exact
-// FP32 subtraction (packed, two per instruction) instead of an integer-to-float conversion.
-constexpr uint32_t kAccumulatorBias = 0x4B400000u;
-constexpr float kAccumulatorBiasValue = 12582912.0f;
-
-// Sixteen registers holding the bias, for tmem_st_16x256b_x4.  The values come out of an
-// asm statement so that the compiler keeps one register block instead of rebuilding it in
-// front of every store.
-__device__ __forceinline__ void make_bias_block(uint32_t (&r)[16]) {
-#pragma unroll
-  for (int i = 0; i < 16; ++i) asm volatile("mov.u32 %0, %1;" : "=r"(r[i]) : "n"(0x4B400000));
 }
 
 // ---------------------------------------------------------------- misc

@@ -11,7 +11,10 @@ Signature, validation and stage semantics follow the reference's ``src/grain_gem
 4. top-k weighted combine                                       (``gg_moe_combine``)
 
 Intermediates use the ragged sorted-slot layout (``[S, I]`` INT8 + ``[S, I/256]`` scales,
-``[S, H]`` expert outputs); there is no expert-expanded or capacity-padded buffer.
+``[S, H]`` expert outputs), never a capacity-padded ``[E, C, *]`` one.  Stage 2 has two ways
+to fetch token rows: by default a copy kernel first writes them in sorted-slot order (one
+tiled TMA box per operand slab, the faster way on B200); ``variant='tensor_core_gather'``
+reads ``hidden_states`` directly with TMA row gathers, without any copy in expert order.
 """
 
 from __future__ import annotations
@@ -199,11 +202,13 @@ def prepare_tiles(routes, tile_rows):
 
 
 def gate_up_swiglu_quantize(hidden_states, scale_x, w1_linear, scale_gate_up, routes, *,
-                            output_dtype=torch.bfloat16, gate_up_layout="split"):
+                            output_dtype=torch.bfloat16, gate_up_layout="split", row_gather=False):
     """Stage 2: ``qh[S, I]`` INT8 and ``sh[S, I/256]`` FP32 for the valid sorted slots.
 
     ``w1_linear`` is the contiguous Linear view ``[E, 2I, H]``.  Rows of invalid slots are
-    left unwritten; nothing downstream reads them.
+    left unwritten; nothing downstream reads them.  ``row_gather`` makes the fused kernel read
+    the token rows straight from ``hidden_states`` by TMA row gathers instead of from a copy in
+    sorted order (same bits; the copy is faster on B200 and is the default).
     """
     lib = _loader.library()
     experts, twice_intermediate, hidden = w1_linear.shape
@@ -213,7 +218,8 @@ def gate_up_swiglu_quantize(hidden_states, scale_x, w1_linear, scale_gate_up, ro
     qh = torch.empty((slots, intermediate), dtype=torch.int8, device=device)
     sh = torch.empty((slots, intermediate // 256), dtype=torch.float32, device=device)
     with torch.cuda.device(device):
-        scratch_bytes = lib.gg_moe_gate_up_scratch_bytes(slots, hidden, intermediate, routes.tile_rows)
+        scratch_bytes = lib.gg_moe_gate_up_scratch_bytes(slots, hidden, intermediate,
+                                                         routes.tile_rows, int(row_gather))
     scratch = torch.empty((max(scratch_bytes, 16),), dtype=torch.uint8, device=device)
     _loader.check(lib.gg_moe_gate_up(
         _loader.pointer(hidden_states), _loader.pointer(scale_x), _loader.pointer(w1_linear),
@@ -222,7 +228,7 @@ def gate_up_swiglu_quantize(hidden_states, scale_x, w1_linear, scale_gate_up, ro
         _loader.pointer(routes.tile_row), routes.tile_expert.numel(), routes.tile_rows,
         _loader.pointer(qh), _loader.pointer(sh), _loader.pointer(scratch),
         routes.tokens, routes.top_k, experts, hidden, intermediate,
-        int(gate_up_layout == "interleaved"), _loader.OUT_DTYPE[output_dtype],
+        int(gate_up_layout == "interleaved"), _loader.OUT_DTYPE[output_dtype], int(row_gather),
         _loader.stream_pointer(device)), "gg_moe_gate_up")
     return qh, sh
 
@@ -305,14 +311,15 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
     Eager calls read three integers back to reject unmasked ids outside ``[0,E)`` with a
     ``ValueError`` (the copy overlaps the remaining stages; the call returns or raises once
     routing has run); under CUDA-graph capture that check is skipped.  ``variant`` is
-    ``'auto'``, ``'tensor_core'`` or ``'cuda_core'`` (tests and benchmarks).
+    ``'auto'``, ``'tensor_core'``, ``'tensor_core_gather'`` (the fused Gate/Up kernel fetches
+    token rows by TMA row gathers, no copy in expert order) or ``'cuda_core'``.
     """
     tokens, hidden, intermediate, experts, top_k = _validate(
         hidden_states, w_gate_up, w_down, topk_weights, topk_ids,
         scale_x, scale_gate_up, scale_down, token_mask, group_size, activation, backend,
         output_dtype, gate_up_layout)
-    if variant not in ("auto", "tensor_core", "cuda_core"):
-        raise ValueError("variant must be 'auto', 'tensor_core' or 'cuda_core'")
+    if variant not in ("auto", "tensor_core", "tensor_core_gather", "cuda_core"):
+        raise ValueError("variant must be 'auto', 'tensor_core', 'tensor_core_gather' or 'cuda_core'")
     with torch.cuda.device(hidden_states.device):
         capturing = torch.cuda.is_current_stream_capturing()
         if tokens == 0:
@@ -320,8 +327,8 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
         w1_linear = w_gate_up.transpose(-2, -1)
         w2_linear = w_down.transpose(-2, -1)
         aligned = _tensor_core_ready(hidden_states, w_gate_up, w_down)
-        if variant == "tensor_core" and not aligned:
-            raise ValueError("variant='tensor_core' requires 16-byte-aligned hidden_states and weights")
+        if variant.startswith("tensor_core") and not aligned:
+            raise ValueError(f"variant='{variant}' requires 16-byte-aligned hidden_states and weights")
         tile_rows = (CUDA_CORE_TILE_ROWS if variant == "cuda_core" or not aligned
                      else TENSOR_CORE_TILE_ROWS)
         routes = prepare_routes(topk_ids, experts, token_mask, tile_rows=tile_rows)
@@ -332,7 +339,8 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
         readback = None if capturing else _statistics_readback(routes.statistics)
         qh, sh = gate_up_swiglu_quantize(
             hidden_states, scale_x, w1_linear, scale_gate_up, routes,
-            output_dtype=output_dtype, gate_up_layout=gate_up_layout)
+            output_dtype=output_dtype, gate_up_layout=gate_up_layout,
+            row_gather=variant == "tensor_core_gather")
         expert_output = down_projection(qh, sh, w2_linear, scale_down, routes,
                                         output_dtype=output_dtype)
         out = combine(expert_output, topk_weights, routes, output_dtype=output_dtype)

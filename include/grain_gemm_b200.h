@@ -191,21 +191,30 @@ int gg_moe_silu_table(void* table, int out_dtype, void* stream);
  * w1: Linear [E,2I,H] contiguous int8; scale_w1: [E,H/256,2I] fp32.  interleaved != 0 means
  * the 2I dimension is ordered [g0,u0,g1,u1,...].  tile_rows must be the value given to
  * gg_moe_tiles: 128 selects the fused tensor-core kernel (needs 16-byte aligned x and w1),
- * 32 the CUDA-core path.  gate_up_scratch must hold gg_moe_gate_up_scratch_bytes() bytes
- * (16-byte aligned): for the fused kernel the 256 KiB SiLU table only - the kernel reads the
- * original x and scale_x rows by token index (TMA row gathers straight into shared memory),
- * there is no copy of the activations in expert order; for the CUDA-core path the [S,2I]
- * gate/up matrix of out_dtype.
+ * 32 the CUDA-core path.  The fused kernel has two ways to fetch the token rows of a tile:
+ *   row_gather != 0  straight from x[T,H] and scale_x by token index (order[slot] / R): 32 TMA
+ *                    row gathers (cp.async.bulk.tensor tile::gather4, four rows each, per-CTA,
+ *                    no multicast) fill a 128-row operand slab in shared memory; no copy of the
+ *                    activations in expert order exists anywhere;
+ *   row_gather == 0  a small copy kernel first writes the rows and their scales in sorted-slot
+ *                    order into the scratch, so that a slab is one tiled TMA box.  Measured on
+ *                    B200 this is the faster of the two (the TMA unit processes a gather of
+ *                    four rows no faster than a whole 128-row box), so the Python layer uses
+ *                    it by default.
+ * Both give identical bits.  gate_up_scratch must hold gg_moe_gate_up_scratch_bytes() bytes
+ * (16-byte aligned): the 256 KiB SiLU table, preceded for row_gather == 0 by the sorted rows
+ * [S,H] and scales [S,H/256]; for the CUDA-core path the [S,2I] gate/up matrix of out_dtype.
  * Replaces ragged_gemm + swiglu_quantize (src/grain_gemm/moe.py:298-304) and
  * grain_moe_gather_launch / grain_moe_interleaved_launch
  * (csrc/sm110/int8_g256_moe_gather.cu:380, int8_g256_moe_interleaved.cu:372).
  */
-size_t gg_moe_gate_up_scratch_bytes(int assignments, int hidden, int intermediate, int tile_rows);
+size_t gg_moe_gate_up_scratch_bytes(int assignments, int hidden, int intermediate, int tile_rows,
+                                    int row_gather);
 int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const void* scale_w1,
                    const void* order, const void* offsets, const void* tile_expert,
                    const void* tile_row, int tile_capacity, int tile_rows, void* q, void* s,
                    void* gate_up_scratch, int tokens, int top_k, int experts, int hidden,
-                   int intermediate, int interleaved, int out_dtype, void* stream);
+                   int intermediate, int interleaved, int out_dtype, int row_gather, void* stream);
 
 /*
  * Down projection over the sorted slots: expert_out[S,H] (out_dtype) from q[S,I], s[S,I/256],
