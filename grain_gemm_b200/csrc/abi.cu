@@ -210,10 +210,7 @@ static int launch_tc_kernel(const CUtensorMap& map_a, const CUtensorMap& map_b,
   return static_cast<int>(error);
 }
 
-#ifndef GG_PROMO_WARPS
-#define GG_PROMO_WARPS 8
-#endif
-template <int kCtaGroup, int BN, int kStages, bool kGrouped, int kPromoWarps = GG_PROMO_WARPS>
+template <int kCtaGroup, int BN, int kStages, bool kGrouped, int kPromoWarps = 8>
 static int launch_tc_dtype(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmTcParams& p,
                            int out_dtype, cudaStream_t stream) {
   switch (out_dtype) {

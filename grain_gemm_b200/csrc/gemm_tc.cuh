@@ -13,10 +13,12 @@
 //   warp 9      MMA issuer: tcgen05.mma kind::i8, K = 32 per instruction, INT32 accumulators in
 //               TMEM, two accumulator buffers of BN columns.  The first MMA of every K group
 //               overwrites the buffer, the last one commits it to the promotion warps.
-//   scale warp  copies each group's scale_b columns and scale_a rows into a shared-memory ring
-//   warps 0-7   promotion: drain the group's INT32 tile with tcgen05.ld (thread = row,
-//               registers = columns), multiply by sa*sb, add into FP32 registers while the
-//               tensor core works on the next group; at the end of the tile cast and store.
+//   scale warp  cp.async of each group's scale_b columns and scale_a rows into a shared-memory
+//               ring, a whole ring ahead of the promotion warps
+//   warps 0-7   promotion: drain the group's INT32 tile with tcgen05.ld in a matrix-fragment
+//               layout (a thread owns 4 rows x 32 columns of its warp's 32 x 128 region),
+//               multiply by sa*sb, add into FP32 registers while the tensor core works on the
+//               next group; at the end of the tile cast, exchange inside quads and store.
 // kCtaGroup == 2 pairs two CTAs (a 2-CTA cluster) on a 256 x BN tile: each CTA loads its own
 // 128 rows of A and its own half of B, the leader CTA issues cta_group::2 MMAs that read both
 // CTAs' shared memory and write both CTAs' TMEM.
@@ -41,14 +43,6 @@ namespace gg {
 #endif
 #ifndef GG_AUX_REGS
 #define GG_AUX_REGS 64
-#endif
-// TMEM drain layout of the GEMM kernel (see FragmentLayout); 0 keeps the pairs layout for
-// measurements.
-#ifndef GG_EXP
-#define GG_EXP 0
-#endif
-#ifndef GG_GEMM_FRAGMENT_QUADS
-#define GG_GEMM_FRAGMENT_QUADS 1
 #endif
 
 struct GemmTcParams {
@@ -185,18 +179,23 @@ __device__ __forceinline__ int ring_row_position(int r) { return (r & 7) * 4 + (
 // The eight column scales (four pairs) of this thread for one 32-column block.
 __device__ __forceinline__ void load_column_scales(const float* block_base, int quad,
                                                    float2 (&sb)[4]) {
-  const float4 lo = *reinterpret_cast<const float4*>(block_base + quad * 8);
-  const float4 hi = *reinterpret_cast<const float4*>(block_base + quad * 8 + 4);
+  const uint32_t address = smem_u32(block_base + quad * 8);
+  const float4 lo = lds_f32x4(address);
+  const float4 hi = lds_f32x4(address + 16);
   sb[0] = make_float2(lo.x, lo.y);
   sb[1] = make_float2(lo.z, lo.w);
   sb[2] = make_float2(hi.x, hi.y);
   sb[3] = make_float2(hi.z, hi.w);
 }
-// The four row scales of this thread (rows fragment_row + 8j of the warp's 32 rows).
+// The four row scales of this thread (rows fragment_row + 8j of the warp's 32 rows), each
+// doubled into the register pair the packed multiply takes; built once per K group.
 __device__ __forceinline__ void load_row_scales(const float* warp_rows_base, int fragment_row,
-                                                float (&sa)[4]) {
-  const float4 v = *reinterpret_cast<const float4*>(warp_rows_base + fragment_row * 4);
-  sa[0] = v.x; sa[1] = v.y; sa[2] = v.z; sa[3] = v.w;
+                                                float2 (&sa)[4]) {
+  const float4 v = lds_f32x4(smem_u32(warp_rows_base + fragment_row * 4));
+  sa[0] = make_float2(v.x, v.x);
+  sa[1] = make_float2(v.y, v.y);
+  sa[2] = make_float2(v.z, v.z);
+  sa[3] = make_float2(v.w, v.w);
 }
 
 template <FragmentLayout kLayout>
@@ -210,13 +209,11 @@ __device__ __forceinline__ void tmem_ld_fragment(uint32_t taddr, uint32_t (&r)[1
 // block and used for both 16-row fragments.  Registers: pairs layout 4j + {0,1} = low pair j,
 // 4j + {2,3} = high pair j; quads layout 4j + {0,2} = low pair j, 4j + {1,3} = high pair j.
 template <FragmentLayout kLayout>
-__device__ __forceinline__ void promote_fragment(const uint32_t (&partial)[16], float sa_low,
-                                                 float sa_high, const float2 (&sb)[4],
+__device__ __forceinline__ void promote_fragment(const uint32_t (&partial)[16], float2 sa_low2,
+                                                 float2 sa_high2, const float2 (&sb)[4],
                                                  float2* acc_low, float2* acc_high) {
   constexpr int kLowY = kLayout == kFragmentPairs ? 1 : 2;
   constexpr int kHighX = kLayout == kFragmentPairs ? 2 : 1;
-  const float2 sa_low2 = make_float2(sa_low, sa_low);
-  const float2 sa_high2 = make_float2(sa_high, sa_high);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const float2 low = make_float2(__int2float_rn(static_cast<int>(partial[4 * j + 0])),
@@ -266,7 +263,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr int kNC = Shape::kColumnsPerThread;   // columns owned by one promotion thread
   constexpr int kProducerWarp = kPromoWarps, kMmaWarp = kPromoWarps + 1;
   constexpr int kScaleWarp = kPromoWarps + 2;
-  constexpr FragmentLayout kLayout = GG_GEMM_FRAGMENT_QUADS ? kFragmentQuads : kFragmentPairs;
+  constexpr FragmentLayout kLayout = kFragmentQuads;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -349,9 +346,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (leader) {
           uint8_t* a_dst = stage_base + stage * Shape::kStageBytes;
           uint8_t* b_dst = a_dst + Shape::kABytes;
-          if constexpr ((GG_EXP & 8) != 0) {
-            if (cta_rank == 0) mbar_arrive(&full_bar[stage]);
-          } else if constexpr (kCtaGroup == 1) {
+          if constexpr (kCtaGroup == 1) {
             mbar_expect_tx(&full_bar[stage], Shape::kStageBytes);
             tma_load_2d(a_dst, &map_a, &full_bar[stage], x, row_a);
             tma_load_2d(b_dst, &map_b, &full_bar[stage], x, row_b);
@@ -476,7 +471,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
-  } else if (warp == kScaleWarp && !kDump && (GG_EXP & 4) == 0) {
+  } else if (warp == kScaleWarp && !kDump) {
     // ------------------------------------------------------------ scale staging warp
     // Copies each group's scale_b columns and scale_a rows into a shared-memory ring with
     // asynchronous 4-byte copies (cp.async) that land directly in the order the promotion
@@ -641,12 +636,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // instructions below always see a converged warp, also after a wait has run out.
       for (int g = 0; g < groups; ++g, ++group_sequence) {
         // This group's scales, staged by the scale warp.
-        if (ok && (GG_EXP & 4) == 0) {
+        if (ok) {
           ok = mbar_wait_warp(&scale_full_bar[scale_slot], scale_phase, kSiteScaleFull, abort_flag);
         }
         const float* scale_slot_base = scale_ring + scale_slot * Shape::kScaleSlotFloats;
-        float sa[4] = {1.f, 1.f, 1.f, 1.f};
-        if ((GG_EXP & 4) == 0) load_row_scales(scale_slot_base + BN + quarter * 32, fragment_row, sa);
+        float2 sa[4];
+        load_row_scales(scale_slot_base + BN + quarter * 32, fragment_row, sa);
         const uint32_t buffer = group_sequence & 1u;
         if (ok) {
           ok = mbar_wait_warp(&tmem_full_bar[buffer], (group_sequence >> 1) & 1u,
@@ -662,18 +657,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t partial_a[16], partial_b[16];
         float2 sb[4];
         if (ok) {
-          if ((GG_EXP & 2) == 0) tmem_ld_fragment<kLayout>(taddr_low, partial_a);
+          tmem_ld_fragment<kLayout>(taddr_low, partial_a);
 #pragma unroll
           for (int fragment = 0; fragment < 2 * kBlocks; ++fragment) {
             const int block = fragment >> 1;
             const int high_half = fragment & 1;
-            if (!high_half && (GG_EXP & 4) == 0) load_column_scales(sb_columns + block * 32, lane & 3, sb);
-            if ((GG_EXP & 2) == 0) tmem_ld_wait();
+            if (!high_half) load_column_scales(sb_columns + block * 32, lane & 3, sb);
+            tmem_ld_wait();
             if (fragment + 1 < 2 * kBlocks) {
               const uint32_t next = ((fragment + 1) & 1 ? taddr_high : taddr_low) +
                                     ((fragment + 1) >> 1) * 32;
-              if ((GG_EXP & 2) != 0) {}
-              else if (fragment & 1) tmem_ld_fragment<kLayout>(next, partial_a);
+              if (fragment & 1) tmem_ld_fragment<kLayout>(next, partial_a);
               else tmem_ld_fragment<kLayout>(next, partial_b);
             } else {
               // All of this warp's TMEM accesses for the buffer are done: hand it back.
@@ -684,8 +678,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 else mbar_arrive_cluster(&tmem_empty_bar[buffer], 0);
               }
             }
-            if ((GG_EXP & 1) != 0) {
-            } else if (fragment & 1) {
+            if (fragment & 1) {
               promote_fragment<kLayout>(partial_b, sa[2], sa[3], sb, &acc[2][block * 4],
                                       &acc[3][block * 4]);
             } else {
@@ -696,7 +689,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         // Every lane has consumed the slot's values (they fed the arithmetic above).
         __syncwarp();
-        if (lane == 0 && (GG_EXP & 4) == 0) mbar_arrive(&scale_empty_bar[scale_slot]);
+        if (lane == 0) mbar_arrive(&scale_empty_bar[scale_slot]);
         if (++scale_slot == Shape::kScaleSlots) {
           scale_slot = 0;
           scale_phase ^= 1u;

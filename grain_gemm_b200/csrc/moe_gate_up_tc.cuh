@@ -7,17 +7,19 @@
 //   h[c]      = silu(gate[c]) * up[c]                       (FP32, every operation rounded)
 //   scale     = max(max_c |h[c]|, 1e-12) / 127 ;  q[c] = clamp(nearbyint(h[c]/scale), +-127)
 // i.e. src/grain_gemm/kernels/moe.py:359-393 (ragged GEMM with SOURCE_IS_TOKEN) followed by
-// :564-601 (SwiGLU + requantisation) of the reference, without the [S, 2I] intermediate.  The
-// token rows are first copied once into sorted-slot order (gather_rows_kernel), so that every
-// operand tile of this kernel arrives by TMA: gathering rows with 16-byte cp.async inside the
-// kernel re-fetched each row tile for every 128-channel block and loaded the load/store
-// pipe, which the promotion warps also need.
+// :564-601 (SwiGLU + requantisation) of the reference, without the [S, 2I] intermediate.
+// Token rows reach shared memory in one of two ways (template parameter kGather): straight from
+// x[T, H] by token index with TMA row gathers (tile::gather4, 32 per 128-row operand slab, no
+// copy of the activations in expert order), or as one tiled TMA box per slab from a copy of the
+// rows in sorted-slot order that gather_rows_kernel writes first.  Both give the same bits;
+// on B200 the copy is faster (the TMA unit takes about as long for a four-row gather as for a
+// whole box), so it is what the Python layer picks by default.
 //
 // Work item = (128-row tile of one expert, 256-channel group), processed as two sub-tiles of
 // 128 channels; a sub-tile is one N = 256 accumulator (128 gate + 128 up columns) in TMEM.
-//   warp 8    TMA producer: per stage one box of sorted activation rows, two weight boxes
+//   warp 8    TMA producer: per stage the activation rows (one box, or 32 row gathers) and two weight boxes
 //   warp 9    MMA issuer (tcgen05.mma kind::i8, two TMEM buffers)
-//   warp 10   scale staging (column and row scales of each K group into a shared-memory ring)
+//   warp 10   scale staging (cp.async of each K group's column and row scales into a shared-memory ring)
 //   warps 0-7 promotion per K group, then SwiGLU (silu by table lookup); the first sub-tile's h
 //             is parked in shared memory until the second sub-tile supplies the other half of
 //             the row maximum.
@@ -376,7 +378,7 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             ok = mbar_wait_warp(&scale_full_bar[scale_slot], scale_phase, kSiteScaleFull, abort_flag);
           }
           const float* slot = sb_ring + scale_slot * Shape::kRingFloats;
-          float sa[4];
+          float2 sa[4];
           load_row_scales(slot + BN + quarter * 32, fragment_row, sa);
           const uint32_t buffer = group_sequence & 1u;
           if (ok) {

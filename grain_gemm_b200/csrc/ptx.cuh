@@ -168,6 +168,16 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, u
   return __all_sync(0xffffffffu, got);
 }
 
+// 16-byte shared-memory load by 32-bit shared address (a pointer that went through integer
+// arithmetic is a generic pointer to the compiler, which then emits generic loads).
+__device__ __forceinline__ float4 lds_f32x4(uint32_t smem_address) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(smem_address));
+  return v;
+}
+
 // ---------------------------------------------------------------- cp.async (scale staging)
 
 // Asynchronous 4-byte copy global -> shared; `valid == false` writes zero without reading.
