@@ -10,12 +10,15 @@ compute and a copy-out stream (two device buffer sets), so the rate is that of t
 
 N > 1 (``torchrun``): the GEMM is sharded along N with no data-path collective (every rank
 owns its own 8192-column block of B and of C; A and scale_a are replicated), weak scaling;
-the MoE FFN timed beside it (``--moe-config``, reported under ``"moe"``) is expert-parallel
-with NCCL all-to-all for dispatch and combine.
+the MoE FFN timed beside it (``--moe-config``, reported under ``"moe"``) is expert-parallel:
+token rows and results travel through peer memory from inside the dispatch and Down kernels
+(``PeerExchange``), with the NCCL all-to-all path timed next to it (``nccl_all_to_all_ms``).
+The ``moe`` block carries its own roofline, CPU baseline, end-to-end figure, per-phase times
+and, at N > 1, a bit-identity check of the expert-parallel result against one GPU.
 
 ``--impl reference`` times the reference's CPU path for the same metric: the CPU oracle
 (``oracle/``, a restatement of the reference's arithmetic; the reference ships no compiled
-CPU implementation) on a bounded row sample of the same workload, all host threads.
+CPU implementation) on the whole workload, all host threads.
 """
 
 from __future__ import annotations
@@ -57,6 +60,8 @@ def parse():
     parser.add_argument("--variant", default="auto")
     parser.add_argument("--skip-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
+    parser.add_argument("--skip-sustained", action="store_true")
+    parser.add_argument("--skip-library-probe", action="store_true")
     return parser.parse_args()
 
 
@@ -153,12 +158,23 @@ def gemm_bytes(m, n, k, group, out_bytes=2):
     return m * k + n * k + 4 * m * groups + 4 * groups * n + out_bytes * m * n
 
 
+def use_all_host_threads():
+    """The launcher of multi-rank runs exports OMP_NUM_THREADS=1; the CPU arms use every core.
+    Must run before the oracle library (OpenMP) is loaded."""
+    cores = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    torch.set_num_threads(cores)
+    return cores
+
+
 def cpu_gemm_sample(m, n, k, group, budget_seconds=10.0):
-    """Times the CPU oracle on a row sample of the workload sized for about `budget_seconds`
-    of work; returns (TOPS, seconds, rows, threads)."""
+    """Times the CPU oracle on the workload, or on a row sample sized for about
+    `budget_seconds` of work when the whole of it would take longer; returns
+    (TOPS, seconds, rows, threads)."""
+    use_all_host_threads()
     from oracle import cpu as oracle
     probe_rows = 8
-    a, w, scale_a, scale_b = make_gemm_inputs(min(m, 4096), n, k, group, 2026, "cpu")
+    a, w, scale_a, scale_b = make_gemm_inputs(m, n, k, group, 2026, "cpu")
     b = w.t()
     start = time.perf_counter()
     oracle.int8_gemm(a[:probe_rows], b, scale_a[:probe_rows], scale_b, group, torch.bfloat16)
@@ -177,11 +193,12 @@ def run_reference_arm(args, rank):
     m, n, k, g = args.m, args.n, args.k, args.group_size
     samples = []
     for _ in range(max(1, min(args.steps, 3))):
-        samples.append(cpu_gemm_sample(m, n, k, g, budget_seconds=8.0))
+        samples.append(cpu_gemm_sample(m, n, k, g, budget_seconds=30.0))
     samples.sort(key=lambda item: item[0])
     value, seconds, rows, threads = samples[len(samples) // 2]
     times = samples
-    sample = f"{rows} rows of A against the full B (N={n}, K={k}); TOPS = 2*rows*N*K/t"
+    sample = (f"all {rows} rows" if rows == m else f"{rows} of {m} rows of A") + \
+        f" against the full B (N={n}, K={k}); TOPS = 2*rows*N*K/t"
     line = {
         "impl": "reference", "metric": "g256_gemm_effective_int8_tops", "value": value,
         "unit": "TOPS", "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
@@ -237,9 +254,48 @@ class HostPipeline:
         compute.wait_stream(self.copy_in)
 
 
+# Per-launch DRAM traffic of the two MoE GEMM stages on the large configuration, scaled from the
+# ncu captures of one rank's share (T = 2048, 32 experts; profiles/): traffic there is weight
+# dominated and grows with the number of experts touched, i.e. by 8 for all 256 experts.
+MOE_NCU_TRAFFIC_BYTES = {"large": {"gate_up": 8 * 1.15e9, "down": 8 * 0.60e9}}
+
+
+def cpu_moe_sample(name, case, device, experts_sampled=4):
+    """Times the CPU oracle on the assignments of the first `experts_sampled` experts of the
+    workload (their token rows through Gate/Up, SwiGLU, requantisation and Down), all host
+    threads; returns (tokens/s equivalent, seconds, assignments, threads)."""
+    use_all_host_threads()
+    from oracle import cpu as oracle
+    config = bench_moe_config(name)
+    ids = case["topk_ids"].cpu()
+    token, slot = torch.nonzero(ids < experts_sampled, as_tuple=True)
+    if token.numel() == 0:
+        return None
+    sub = dict(
+        hidden_states=case["hidden_states"][token.to(device)].cpu(),
+        scale_x=case["scale_x"][token.to(device)].cpu(),
+        topk_weights=torch.ones((token.numel(), 1)),
+        topk_ids=ids[token, slot].reshape(-1, 1).long(),
+        w_gate_up=case["w_gate_up"][:experts_sampled].cpu(),
+        w_down=case["w_down"][:experts_sampled].cpu(),
+        scale_gate_up=case["scale_gate_up"][:experts_sampled].cpu(),
+        scale_down=case["scale_down"][:experts_sampled].cpu(),
+        gate_up_layout=case.get("gate_up_layout", "split"))
+    start = time.perf_counter()
+    oracle.moe_ffn(**sub)
+    seconds = time.perf_counter() - start
+    assignments = int(token.numel())
+    return assignments / config["top_k"] / seconds, seconds, assignments, oracle.threads()
+
+
+def bench_moe_config(name):
+    import bench_moe
+    return bench_moe.CONFIGS[name]
+
+
 def run_moe(args, rank, world, device, barrier):
-    """Times the MoE FFN: single GPU at world == 1, expert parallel (NCCL all-to-all) beyond.
-    Returns the rank-0 report (None on other ranks)."""
+    """Times the MoE FFN: single GPU at world == 1, expert parallel beyond (peer-memory exchange;
+    the NCCL all-to-all path is timed beside it).  Returns the rank-0 report (None elsewhere)."""
     import torch.distributed as dist
 
     import bench_moe
@@ -248,23 +304,77 @@ def run_moe(args, rank, world, device, barrier):
     name = args.moe_config
     config = bench_moe.CONFIGS[name]
     case = bench_moe.make_case(name, device, rank=rank, world=world)
+    local_tokens = config["tokens"] // world
+    workspace = moe.MoEWorkspace()
+    exchange = None
+    if world > 1:
+        exchange = distributed.PeerExchange.create(
+            dist.group.WORLD, capacity=local_tokens, hidden=config["hidden"],
+            top_k=config["top_k"], local_experts=config["experts"] // world)
 
-    def step(tensors):
+    def step(tensors, marks=None, nccl=False):
         if world == 1:
-            return moe.moe_ffn(**tensors)
-        return distributed.moe_ffn_expert_parallel(**tensors, num_experts=config["experts"])
+            return moe.moe_ffn(**tensors, workspace=workspace)
+        return distributed.moe_ffn_expert_parallel(
+            **tensors, num_experts=config["experts"], exchange=None if nccl else exchange,
+            marks=marks)
+
+    def timed(loop_steps, **kwargs):
+        for _ in range(3):
+            step(case, **kwargs)
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(loop_steps):
+            step(case, **kwargs)
+        stop.record()
+        barrier()
+        value = torch.tensor([start.elapsed_time(stop) / loop_steps], device=device)
+        if world > 1:
+            dist.all_reduce(value, op=dist.ReduceOp.MAX)
+        return float(value.item())
 
     steps = max(1, args.moe_steps)
-    for _ in range(3):
-        step(case)
-    barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(steps):
-        step(case)
-    stop.record()
-    barrier()
-    elapsed = torch.tensor([start.elapsed_time(stop) / steps], device=device)
+    with ClockSampler(device.index) as sampler:
+        ms = timed(steps)
+    nccl_ms = timed(steps, nccl=True) if world > 1 else None
+
+    # Phase times of the expert-parallel step (rank 0's events; no extra synchronisation).
+    phases = None
+    if world > 1:
+        names = ["plan_and_dispatch", "count_all_gather", "local_experts", "results_home_all_reduce",
+                 "combine"]
+        totals = [0.0] * len(names)
+        for _ in range(steps):
+            marks = []
+            step(case, marks=marks)
+            torch.cuda.synchronize()
+            for index in range(len(names)):
+                totals[index] += marks[index].elapsed_time(marks[index + 1])
+        phases = {n: t / steps for n, t in zip(names, totals)}
+        barrier()
+
+    # Bit identity of the expert-parallel result with one GPU, on a problem small enough for
+    # every rank to hold all experts (outside the timed regions).
+    identical = None
+    if world > 1:
+        bench_moe.CONFIGS["ep_check"] = dict(tokens=768, hidden=1024, inter=512, experts=16, top_k=4,
+                                             layout=config["layout"], biased=True)
+        if 768 % world == 0 and 16 % world == 0:
+            small = bench_moe.make_case("ep_check", device, rank=rank, world=world)
+            whole = bench_moe.make_case("ep_check", device)
+            rows = slice(rank * (768 // world), (rank + 1) * (768 // world))
+            single = moe.moe_ffn(**whole)[rows]
+            check = distributed.PeerExchange.create(dist.group.WORLD, capacity=768 // world,
+                                                    hidden=1024, top_k=4, local_experts=16 // world)
+            via_peers = distributed.moe_ffn_expert_parallel(**small, num_experts=16, exchange=check)
+            via_nccl = distributed.moe_ffn_expert_parallel(**small, num_experts=16)
+            same = torch.tensor([int(torch.equal(via_peers, single) and torch.equal(via_nccl, single))],
+                                device=device)
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            identical = bool(same.item())
+            barrier()
+            check.close()
 
     # End to end: the per-token inputs come from pinned host memory, the result goes back.
     token_names = ("hidden_states", "scale_x", "topk_weights", "topk_ids")
@@ -279,34 +389,73 @@ def run_moe(args, rank, world, device, barrier):
     pipeline = HostPipeline([host[n] for n in token_names], host_out, from_device_inputs, device)
     pipeline.run(2)
     barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     pipeline.run(steps, first=2)
     stop.record()
     barrier()
     e2e_elapsed = torch.tensor([start.elapsed_time(stop) / steps], device=device)
     if world > 1:
-        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
         dist.all_reduce(e2e_elapsed, op=dist.ReduceOp.MAX)
     stages = bench_moe.time_stages(case, steps=3, warmup=1) if world == 1 else None
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        cpu = cpu_moe_sample(name, case, device)
+    if exchange is not None:
+        barrier()
+        exchange.close()
     if rank != 0:
         return None
-    ms, e2e_ms = float(elapsed.item()), float(e2e_elapsed.item())
+    e2e_ms = float(e2e_elapsed.item())
     tokens = config["tokens"]
+    peaks = measured_peaks()
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    useful_tops = bench_moe.useful_ops(name) / (ms * 1e-3) / 1e12
+    traffic = MOE_NCU_TRAFFIC_BYTES.get(name)
+    roofline = {
+        "bound": "tensor", "achieved": useful_tops / world, "peak": int8_peak, "unit": "TFLOP/s",
+        "frac": useful_tops / world / int8_peak,
+        "traffic": sum(traffic.values()) if traffic else None,
+        "peak_source": f"2 x bf16_tflops burst ({peaks['source']}); MEASURED_PEAKS has no INT8 entry",
+        "algorithmic_ops_per_step": bench_moe.useful_ops(name),
+        "algorithmic_bytes_per_step": bench_moe.algorithmic_bytes(name),
+        "hbm_time_floor_ms": bench_moe.algorithmic_bytes(name) / (peaks["hbm_gbs"] * 1e9) * 1e3 / world,
+    }
+    if stages is not None:
+        t, r, h, i = config["tokens"], config["top_k"], config["hidden"], config["inter"]
+        roofline["stage_frac"] = {
+            "gate_up": 4.0 * t * r * h * i / (stages["gate_up"] * 1e-3) / 1e12 / int8_peak,
+            "down": 2.0 * t * r * h * i / (stages["down"] * 1e-3) / 1e12 / int8_peak,
+            "combine_hbm": (2.0 * t * r * h + 2.0 * t * h) / (stages["combine"] * 1e-3) / 1e9
+            / peaks["hbm_gbs"],
+        }
     report = {
         "metric": "moe_ffn_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": steps, "ms_per_step": ms, "scaling": "strong",
-        "useful_tops": bench_moe.useful_ops(name) / (ms * 1e-3) / 1e12,
+        "useful_tops": useful_tops,
         "config": {"workload": f"moe_{name}", **{k: v for k, v in config.items()},
-                   "parallelism": "single" if world == 1 else f"ep{world}_nccl_all_to_all"},
-        "algorithmic_bytes": bench_moe.algorithmic_bytes(name),
+                   "parallelism": "single" if world == 1 else f"ep{world}_peer_memory_exchange"},
+        "roofline": roofline, "clocks": sampler.summary(),
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": world * sum(t.numel() * t.element_size() for t in host.values()),
                 "d2h_bytes_per_step": world * host_out.numel() * host_out.element_size(),
                 "ms_per_step": e2e_ms},
-        "gpu_launches_per_step": 8 if world == 1 else 13,
+        # route (1 or 3), tiles, row copy, SiLU table, Gate/Up, Down, combine; the
+        # expert-parallel step adds plan, dispatch, row mask and row destinations.
+        "gpu_launches_per_step": 9 if world == 1 else 13,
     }
     if stages is not None:
         report["stage_ms"] = stages
+    if phases is not None:
+        report["phases_ms"] = phases
+        report["nccl_all_to_all_ms"] = nccl_ms
+        report["ep_bit_identical"] = identical
+    if cpu is not None:
+        value, seconds, assignments, threads = cpu
+        report["cpu_baseline"] = {
+            "value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{assignments} assignments (those of the first 4 experts) through Gate/Up, "
+                      f"SwiGLU, requantisation and Down in {seconds:.2f} s; tokens = assignments / top_k"}
     return report
 
 
@@ -376,6 +525,48 @@ def main():
     tops = 2.0 * m * n * world * k / (ms_per_step * 1e-3) / 1e12
     kernel_name = gemm.get_kernel_config(a, b, group_size=g)["variant"]
 
+    # Sustained rate: at least two seconds of back-to-back launches, with its own clock record
+    # (the part runs into its power limit; the burst figure above does not show that).
+    sustained = None
+    if not args.skip_sustained:
+        sustained_steps = max(args.steps, int(2.2 / (ms_per_step * 1e-3)))
+        with ClockSampler(local_rank) as sustained_sampler:
+            barrier()
+            start.record()
+            for _ in range(sustained_steps):
+                step()
+            stop.record()
+            barrier()
+        sustained_ms = start.elapsed_time(stop)
+        if world > 1:
+            reduced = torch.tensor([sustained_ms], device=device)
+            dist.all_reduce(reduced, op=dist.ReduceOp.MAX)
+            sustained_ms = float(reduced.item())
+        sustained_ms /= sustained_steps
+        sustained = {"steps": sustained_steps, "ms_per_step": sustained_ms,
+                     "value": 2.0 * m * n * world * k / (sustained_ms * 1e-3) / 1e12, "unit": "TOPS",
+                     "clocks": sustained_sampler.summary()}
+
+    # Same-box context: the library INT8 GEMM (cuBLASLt through torch._int_mm; INT32 output, no
+    # scales, no promotion), a library call timed the same way.
+    library_probe = None
+    if world == 1 and m > 16 and not args.skip_library_probe:
+        try:
+            for _ in range(3):
+                torch._int_mm(a, b)
+            barrier()
+            start.record()
+            for _ in range(10):
+                torch._int_mm(a, b)
+            stop.record()
+            barrier()
+            probe_ms = start.elapsed_time(stop) / 10
+            library_probe = {"call": "torch._int_mm", "ms_per_step": probe_ms,
+                             "value": 2.0 * m * n * k / (probe_ms * 1e-3) / 1e12, "unit": "TOPS",
+                             "note": "INT32 output, no group scales: context, not the same operator"}
+        except RuntimeError as error:
+            library_probe = {"call": "torch._int_mm", "unavailable": str(error).splitlines()[0][:200]}
+
     # End to end through the public API with host operands.
     e2e = None
     if not args.skip_e2e:
@@ -424,9 +615,6 @@ def main():
         "traffic": NCU_TRAFFIC_BYTES.get(f"gemm_g{g}_m{m}_n{n}_k{k}_bf16"),
         "peak_source": f"2 x bf16_tflops burst ({peaks['source']}); MEASURED_PEAKS has no INT8 entry",
         "frac_of_nominal_4500": per_gpu_tops / 4500.0,
-        # A long back-to-back run reaches the power cap, as the sustained BF16 figure did.
-        "frac_of_2x_bf16_sustained": (per_gpu_tops / (2.0 * peaks["bf16_tflops_sustained"])
-                                      if peaks.get("bf16_tflops_sustained") else None),
         "algorithmic_ops_per_launch": 2.0 * m * n * k,
         "algorithmic_bytes_per_launch": gemm_bytes(m, n, k, g),
         "kernel": kernel_name,
@@ -443,13 +631,23 @@ def main():
     }
     if e2e is not None:
         line["e2e"] = e2e
+    if sustained is not None:
+        if peaks.get("bf16_tflops_sustained"):
+            sustained["frac_of_2x_bf16_sustained"] = (sustained["value"] / world
+                                                      / (2.0 * peaks["bf16_tflops_sustained"]))
+        mhz = sustained["clocks"].get("sm_mhz")
+        sustained["ms_times_median_sm_mhz"] = sustained["ms_per_step"] * mhz if mhz else None
+        line["sustained"] = sustained
+    if library_probe is not None:
+        line["int8_library_probe"] = library_probe
     if moe_result is not None:
         line["moe"] = moe_result
     if world == 1 and not args.skip_cpu_baseline:
         cpu_tops, seconds, rows, threads = cpu_gemm_sample(m, n, k, g)
         line["cpu_baseline"] = {
             "value": cpu_tops, "unit": "TOPS", "cores": threads, "kind": "port",
-            "sample": f"{rows} rows of A against the full B ({seconds:.2f} s); scaled by rows"}
+            "sample": (f"all {rows} rows" if rows == m else f"{rows} of {m} rows of A")
+            + f" against the full B ({seconds:.2f} s)"}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

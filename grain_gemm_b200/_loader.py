@@ -50,7 +50,16 @@ _SIGNATURES = {
     "gg_moe_silu_table": (_INT, [_VOID, _INT, _VOID]),
     "gg_moe_gate_up_scratch_bytes": (_SIZE, [_INT] * 5),
     "gg_moe_gate_up": (_INT, [_VOID] * 8 + [_INT, _INT] + [_VOID] * 3 + [_INT] * 8 + [_VOID]),
-    "gg_moe_down": (_INT, [_VOID] * 7 + [_INT, _INT, _VOID] + [_INT] * 5 + [_VOID]),
+    "gg_moe_down": (_INT, [_VOID] * 7 + [_INT, _INT, _VOID, _VOID] + [_INT] * 5 + [_VOID]),
+    "gg_ep_plan": (_INT, [_VOID, _INT, _VOID] + [_INT] * 5 + [_VOID] * 4),
+    "gg_ep_dispatch": (_INT, [_VOID, _VOID, _VOID, _INT, _VOID, _VOID] + [_INT] * 8 + [_VOID] * 6),
+    "gg_ep_row_mask": (_INT, [_VOID, _INT, _INT, _INT, _VOID, _VOID]),
+    "gg_ep_row_destination": (_INT, [_VOID, _VOID] + [_INT] * 6 + [_VOID] * 5),
+    "gg_peer_alloc": (_INT, [_SIZE, ctypes.POINTER(_VOID)]),
+    "gg_peer_free": (_INT, [_VOID]),
+    "gg_peer_export": (_INT, [_VOID, _VOID]),
+    "gg_peer_import": (_INT, [_VOID, ctypes.POINTER(_VOID)]),
+    "gg_peer_release": (_INT, [_VOID]),
     "gg_moe_combine": (_INT, [_VOID] * 4 + [_INT] * 4 + [_VOID]),
     "gg_device_status": (_INT, [ctypes.POINTER(_INT), _VOID]),
     "gg_selftest_wait_timeout": (_INT, [_LL, _VOID, _VOID]),

@@ -6,12 +6,14 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 #include <mutex>
 
 #include "../../include/grain_gemm_b200.h"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
+#include "moe_ep.cuh"
 #include "moe_gate_up_tc.cuh"
 #include "moe_route.cuh"
 
@@ -720,18 +722,22 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
 
 int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_w2,
                 const void* offsets, const void* tile_expert, const void* tile_row,
-                int tile_capacity, int tile_rows, void* expert_out, int assignments, int experts,
-                int hidden, int intermediate, int out_dtype, void* stream_ptr) {
+                int tile_capacity, int tile_rows, void* expert_out, const void* row_destination,
+                int assignments, int experts, int hidden, int intermediate, int out_dtype,
+                void* stream_ptr) {
   if (assignments <= 0 || experts <= 0 || hidden <= 0 || intermediate <= 0 || intermediate % 256 ||
       tile_capacity <= 0 || (out_dtype != GG_OUT_BF16 && out_dtype != GG_OUT_FP16) || !q || !s ||
-      !w2 || !scale_w2 || !offsets || !tile_expert || !tile_row || !expert_out) {
+      !w2 || !scale_w2 || !offsets || !tile_expert || !tile_row ||
+      (!expert_out && !row_destination) || (row_destination && tile_rows != 128)) {
     return static_cast<int>(cudaErrorInvalidValue);
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   if (tile_rows == 128) {
-    if (!gg::aligned16(q) || !gg::aligned16(w2) || !gg::aligned16(expert_out) || hidden % 8) {
+    if (!gg::aligned16(q) || !gg::aligned16(w2) || !gg::aligned16(expert_out) || hidden % 8 ||
+        !gg::aligned16(row_destination)) {
       return static_cast<int>(cudaErrorInvalidValue);
     }
+    const unsigned long long* destinations = static_cast<const unsigned long long*>(row_destination);
     CUtensorMap map_a, map_b;
     int status = gg::encode_int8_rows(&map_a, q, assignments, intermediate, intermediate, 128);
     if (status) return status;
@@ -757,6 +763,7 @@ int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_
     p.tile_row = static_cast<const int*>(tile_row);
     p.b_rows_per_expert = hidden;
     p.sb_expert_stride = static_cast<long long>(intermediate / 256) * hidden;
+    p.row_destination = destinations;
     if (bn == 256) return gg::launch_tc_dtype<1, 256, 4, true>(map_a, map_b, p, out_dtype, stream);
     if (bn == 128) return gg::launch_tc_dtype<1, 128, 6, true>(map_a, map_b, p, out_dtype, stream);
     return gg::launch_tc_dtype<1, 64, 8, true>(map_a, map_b, p, out_dtype, stream);
@@ -780,6 +787,132 @@ int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_
   p.sb_expert_stride = static_cast<long long>(intermediate / 256) * hidden;
   return gg::launch_simt_dtype<true>(p, tile_capacity, out_dtype, stream);
 }
+
+// ---------------------------------------------------------------- expert-parallel exchange
+
+int gg_ep_plan(const void* ids, int ids_are_i64, const void* mask, int tokens, int top_k,
+               int experts, int world, int local_experts, void* position, void* counts,
+               void* home_inverse, void* stream_ptr) {
+  if (tokens < 0 || top_k <= 0 || experts <= 0 || world <= 0 || world > 1024 ||
+      local_experts <= 0 || static_cast<long long>(local_experts) * world != experts || !counts) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (tokens > 0 && (!ids || !position || !home_inverse)) return static_cast<int>(cudaErrorInvalidValue);
+  gg::EpPlanParams p = {};
+  p.ids = ids; p.ids_are_i64 = ids_are_i64;
+  p.mask = static_cast<const uint8_t*>(mask);
+  p.tokens = tokens; p.top_k = top_k; p.experts = experts; p.world = world;
+  p.local_experts = local_experts;
+  p.position = static_cast<int*>(position);
+  p.counts = static_cast<int*>(counts);
+  p.home_inverse = static_cast<int*>(home_inverse);
+  gg::ep_plan_kernel<<<world, 1024, 0, static_cast<cudaStream_t>(stream_ptr)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gg_ep_dispatch(const void* x, const void* scale_x, const void* ids, int ids_are_i64,
+                   const void* mask, const void* position, int tokens, int top_k, int experts,
+                   int world, int local_experts, int hidden, int rank, int capacity,
+                   const void* recv_x, const void* recv_scale, const void* recv_ids,
+                   const void* recv_src, void* error, void* stream_ptr) {
+  if (tokens < 0 || top_k <= 0 || experts <= 0 || world <= 0 || local_experts <= 0 ||
+      static_cast<long long>(local_experts) * world != experts || hidden <= 0 || hidden % 256 ||
+      rank < 0 || rank >= world || capacity <= 0 || tokens > capacity || !recv_x || !recv_scale ||
+      !recv_ids || !recv_src || !error) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (tokens == 0) return 0;
+  if (!x || !scale_x || !ids || !position || !gg::aligned16(x)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  gg::EpDispatchParams p = {};
+  p.x = static_cast<const int8_t*>(x);
+  p.scale_x = static_cast<const float*>(scale_x);
+  p.ids = ids; p.ids_are_i64 = ids_are_i64;
+  p.mask = static_cast<const uint8_t*>(mask);
+  p.position = static_cast<const int*>(position);
+  p.tokens = tokens; p.top_k = top_k; p.experts = experts; p.world = world;
+  p.local_experts = local_experts; p.hidden = hidden; p.rank = rank; p.capacity = capacity;
+  p.recv_x = static_cast<const unsigned long long*>(recv_x);
+  p.recv_scale = static_cast<const unsigned long long*>(recv_scale);
+  p.recv_ids = static_cast<const unsigned long long*>(recv_ids);
+  p.recv_src = static_cast<const unsigned long long*>(recv_src);
+  p.error = static_cast<int*>(error);
+  const long long pairs = static_cast<long long>(tokens) * world;
+  const long long blocks = (pairs + 7) / 8;
+  const int limit = gg::sm_count() * 8;
+  gg::ep_dispatch_kernel<<<static_cast<int>(blocks < limit ? blocks : limit), 256, 0,
+                           static_cast<cudaStream_t>(stream_ptr)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gg_ep_row_mask(const void* counts_all, int world, int rank, int capacity, void* row_mask,
+                   void* stream_ptr) {
+  if (!counts_all || !row_mask || world <= 0 || rank < 0 || rank >= world || capacity <= 0) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  const long long rows = static_cast<long long>(world) * capacity;
+  const long long blocks = (rows + 255) / 256;
+  const int limit = gg::sm_count() * 4;
+  gg::ep_row_mask_kernel<<<static_cast<int>(blocks < limit ? blocks : limit), 256, 0,
+                           static_cast<cudaStream_t>(stream_ptr)>>>(
+      static_cast<const int*>(counts_all), world, rank, capacity, static_cast<uint8_t*>(row_mask));
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gg_ep_row_destination(const void* order, const void* offsets, int experts, int top_k,
+                          int capacity, int world, int hidden, int out_dtype, const void* recv_src,
+                          const void* home_out, void* row_destination, void* error,
+                          void* stream_ptr) {
+  if (!order || !offsets || !recv_src || !home_out || !row_destination || !error || experts <= 0 ||
+      top_k <= 0 || capacity <= 0 || world <= 0 || hidden <= 0 ||
+      (out_dtype != GG_OUT_BF16 && out_dtype != GG_OUT_FP16)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  const long long slots = static_cast<long long>(world) * capacity * top_k;
+  const long long blocks = (slots + 255) / 256;
+  const int limit = gg::sm_count() * 8;
+  gg::ep_row_destination_kernel<<<static_cast<int>(blocks < limit ? blocks : limit), 256, 0,
+                                  static_cast<cudaStream_t>(stream_ptr)>>>(
+      static_cast<const long long*>(order), static_cast<const int*>(offsets), experts, top_k,
+      capacity, world, hidden, 2, static_cast<const int*>(recv_src),
+      static_cast<const unsigned long long*>(home_out), slots,
+      static_cast<unsigned long long*>(row_destination), static_cast<int*>(error));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---- peer-addressable device memory (set-up time, not on the hot path) -------------------
+
+int gg_peer_alloc(size_t bytes, void** pointer) {
+  if (!pointer || bytes == 0) return static_cast<int>(cudaErrorInvalidValue);
+  void* memory = nullptr;
+  cudaError_t error = cudaMalloc(&memory, bytes);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  error = cudaMemset(memory, 0, bytes);
+  if (error != cudaSuccess) {
+    cudaFree(memory);
+    return static_cast<int>(error);
+  }
+  *pointer = memory;
+  return 0;
+}
+
+int gg_peer_free(void* pointer) { return static_cast<int>(cudaFree(pointer)); }
+
+int gg_peer_export(void* pointer, void* handle) {
+  if (!pointer || !handle) return static_cast<int>(cudaErrorInvalidValue);
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+  return static_cast<int>(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle), pointer));
+}
+
+int gg_peer_import(const void* handle, void** pointer) {
+  if (!handle || !pointer) return static_cast<int>(cudaErrorInvalidValue);
+  cudaIpcMemHandle_t copy;
+  memcpy(&copy, handle, sizeof(copy));
+  return static_cast<int>(cudaIpcOpenMemHandle(pointer, copy, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int gg_peer_release(void* pointer) { return static_cast<int>(cudaIpcCloseMemHandle(pointer)); }
 
 int gg_moe_topk(const void* logits, int in_dtype, int tokens, int experts, int top_k, void* weights,
                 void* ids, int ids_are_i64, void* stream_ptr) {

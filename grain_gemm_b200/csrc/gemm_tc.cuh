@@ -61,6 +61,11 @@ struct GemmTcParams {
   const int* tile_row;         // [tiles_m] first row of each row tile
   long long b_rows_per_expert; // N (rows of the Linear weight per expert)
   long long sb_expert_stride;  // elements between experts in scale_b
+  // Optional (grouped mode): device address of the first element of every output row.  When
+  // set, row r is stored at row_destination[r] instead of c + r * ldc; the addresses may lie in
+  // another GPU's memory (peer mapping), which is how the expert-parallel Down projection
+  // returns each result row to the token's home rank while the GEMM is still running.
+  const unsigned long long* row_destination;
   // Split-K dump mode: the K groups are divided over k_splits work items per output tile and
   // the INT32 group dots go to partials[Q][M][N] instead of being promoted (a second kernel
   // then folds them in group order).  k_splits == 1 and partials == null otherwise.
@@ -707,8 +712,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           const int out_row = first_row + 8 * r;
-          const bool row_stored = out_row < row_limit;
+          bool row_stored = out_row < row_limit;
           OutT* c_row = c + static_cast<long long>(out_row) * p.ldc;
+          if constexpr (kGrouped) {
+            if (p.row_destination != nullptr) {
+              // The table holds the address of the row's first element; 0 = do not store.
+              const unsigned long long destination = row_stored ? p.row_destination[out_row] : 0ull;
+              row_stored = destination != 0ull;
+              c_row = reinterpret_cast<OutT*>(destination);
+            }
+          }
 #pragma unroll
           for (int block = 0; block < kBlocks; ++block) {
             const int col = n0 + col_base + block * 32 + 8 * quad;

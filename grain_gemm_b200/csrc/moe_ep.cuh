@@ -18,7 +18,7 @@
 // travel afterwards in one small all-gather that also orders "all rows have arrived" before
 // the expert kernels start.  Rows beyond a source's count are masked out of the local routing.
 // The Down projection then stores each output row straight into the home rank's home_out
-// (see GemmTcParams::row_dest), so the return trip overlaps the GEMM tile by tile.
+// (see GemmTcParams::row_destination), so the return trip overlaps the GEMM tile by tile.
 #pragma once
 
 #include <stdint.h>
@@ -149,6 +149,8 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchParams
     }
     if (lane == 0) reinterpret_cast<int*>(p.recv_src[d])[row] = token;
   }
+  // The rows are consumed by another GPU after a collective that follows this kernel.
+  __threadfence_system();
 }
 
 // row_mask[s * C + i] = i < counts_all[s][rank]: which rows of the receive area hold a token

@@ -21,9 +21,23 @@ allow without changing their arithmetic:
 
 ``stages`` makes the local computation pluggable so that the exchange logic can be tested on
 CPU ranks (gloo) with a CPU implementation of the stages; the default is the CUDA path.
+
+``moe_ffn_expert_parallel`` has two exchange mechanisms:
+
+* NCCL ``all_to_all_single`` both ways (the default without an ``exchange`` argument);
+* ``PeerExchange``: every rank owns a receive area in device memory that all ranks of the node
+  map (CUDA IPC over NVLink).  The dispatch kernel stores token rows straight into the
+  destination ranks' areas, one small count all-gather orders "everything has arrived", the
+  local experts run on the received rows, and the Down projection stores every result row from
+  inside the GEMM straight into the home rank's area (``row_destination``), so the return trip
+  overlaps the tensor-core work tile by tile; one tiny all-reduce orders "all results are
+  home" before the combine.  No host synchronisation, no per-call allocation, the same bits.
 """
 
 from __future__ import annotations
+
+import ctypes
+from types import SimpleNamespace
 
 import torch
 import torch.distributed as dist
@@ -81,7 +95,7 @@ def _all_to_all_rows(send, send_counts, recv_counts, group):
 def moe_ffn_expert_parallel(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
                             scale_x, scale_gate_up, scale_down, num_experts, token_mask=None,
                             output_dtype=torch.bfloat16, gate_up_layout="split", group=None,
-                            stages=None):
+                            stages=None, exchange=None, marks=None):
     """Expert-parallel FFN for this rank's tokens.
 
     ``hidden_states [T_local, H]``, ``scale_x``, ``topk_weights``, ``topk_ids`` (global expert
@@ -90,8 +104,16 @@ def moe_ffn_expert_parallel(hidden_states, w_gate_up, w_down, topk_weights, topk
     rank's experts ``[rank * E_local, (rank + 1) * E_local)``, in the layouts ``moe_ffn`` takes.
     Returns ``[T_local, H]`` in ``output_dtype``.  Raises ``ValueError`` when an unmasked id is
     outside ``[0, num_experts)`` on any rank, and ``RuntimeError`` when the row counts that
-    arrive do not match the counts that were announced.
+    arrive do not match the counts that were announced.  ``exchange`` (a ``PeerExchange``)
+    replaces the NCCL all-to-alls by stores into peer memory fused into the dispatch and Down
+    kernels; the result is bit-identical.
     """
+    if exchange is not None:
+        if exchange.local_experts * exchange.world != num_experts or \
+                exchange.output_dtype != output_dtype:
+            raise ValueError("the exchange was created for another expert count or output type")
+        return _peer_step(exchange, hidden_states, w_gate_up, w_down, topk_weights, topk_ids,
+                          scale_x, scale_gate_up, scale_down, token_mask, gate_up_layout, marks)
     stages = stages or CudaStages()
     world = dist.get_world_size(group)
     local_experts = w_gate_up.shape[0]
@@ -163,6 +185,276 @@ def moe_ffn_expert_parallel(hidden_states, w_gate_up, w_down, topk_weights, topk
     if valid == 0:
         return torch.zeros((tokens, hidden), dtype=output_dtype, device=device)
     return stages.combine(returned, topk_weights, routes, output_dtype)
+
+
+class _DeviceMemory:
+    """Raw device memory as something ``torch.as_tensor`` accepts (CUDA array interface)."""
+
+    def __init__(self, address, nbytes):
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1",
+                                         "data": (int(address), False), "version": 2}
+
+
+def _align(value, to=256):
+    return (value + to - 1) // to * to
+
+
+class PeerExchange:
+    """One rank's side of the expert-parallel exchange over peer memory.
+
+    Holds this rank's receive area (token rows, scales, local expert indices and home token
+    index of up to ``capacity`` tokens from each of ``world`` ranks, plus the ``home_out``
+    block the other ranks write this rank's results into), the device addresses of every
+    rank's area, and the per-call scratch, all allocated once.  ``capacity`` is the largest
+    number of tokens a rank will pass per call.
+
+    ``PeerExchange.create(group, ...)`` builds the exchange of a process group: the areas are
+    shared between the processes with CUDA IPC handles (one node).  ``PeerExchange.local_ranks``
+    builds ``world`` exchanges inside one process on one GPU, which run the same kernels against
+    the same addresses without any collective; tests use it to cover the whole path on a single
+    GPU.
+    """
+
+    def __init__(self, *, rank, world, capacity, hidden, top_k, local_experts, output_dtype,
+                 device, group=None):
+        from . import _loader, moe
+        self.rank, self.world, self.capacity = rank, world, capacity
+        self.hidden, self.top_k, self.local_experts = hidden, top_k, local_experts
+        self.output_dtype, self.device, self.group = output_dtype, torch.device(device), group
+        rows = world * capacity
+        groups = hidden // 256
+        sections = [("recv_x", rows * hidden), ("recv_scale", rows * groups * 4),
+                    ("recv_ids", rows * top_k * 4), ("recv_src", rows * 4),
+                    ("home_out", capacity * top_k * hidden * 2)]
+        self.offsets, total = {}, 0
+        for name, size in sections:
+            self.offsets[name] = total
+            total += _align(size)
+        self.area_bytes = total
+        self._lib = _loader.library()
+        with torch.cuda.device(self.device):
+            pointer = ctypes.c_void_p()
+            _loader.check(self._lib.gg_peer_alloc(total, ctypes.byref(pointer)), "gg_peer_alloc")
+        self.base = pointer.value
+        self._imported = []
+        area = torch.as_tensor(_DeviceMemory(self.base, total), device=self.device)
+        view = lambda name, size, dtype, shape: area[self.offsets[name]:self.offsets[name] + size] \
+            .view(dtype).view(shape)
+        self.recv_x = view("recv_x", rows * hidden, torch.int8, (rows, hidden))
+        self.recv_scale = view("recv_scale", rows * groups * 4, torch.float32, (rows, groups))
+        self.recv_ids = view("recv_ids", rows * top_k * 4, torch.int32, (rows, top_k))
+        self.recv_src = view("recv_src", rows * 4, torch.int32, (rows,))
+        self.home_out = view("home_out", capacity * top_k * hidden * 2, output_dtype,
+                             (capacity * top_k, hidden))
+        self.recv_src.fill_(0)
+        make = lambda shape, dtype: torch.zeros(shape, dtype=dtype, device=self.device)
+        self.position = make((capacity, world), torch.int32)
+        self.counts = make((world + 1,), torch.int32)
+        self.counts_all = make((world, world + 1), torch.int32)
+        self.home_inverse = make((capacity * top_k,), torch.int32)
+        self.row_mask = make((rows,), torch.uint8)
+        self.row_destination = make((rows * top_k,), torch.int64)
+        self.flags = make((2,), torch.int32)           # [0] = a kernel refused an index
+        self.tables = None
+        self.workspace = moe.MoEWorkspace()
+        self._host = torch.empty((world + 3,), dtype=torch.int32).pin_memory()
+
+    # -- construction ----------------------------------------------------------------------
+
+    def _set_peer_bases(self, bases):
+        table = lambda name: torch.tensor([b + self.offsets[name] for b in bases],
+                                          dtype=torch.int64, device=self.device)
+        self.tables = {name: table(name) for name in self.offsets}
+
+    @classmethod
+    def create(cls, group, *, capacity, hidden, top_k, local_experts,
+               output_dtype=torch.bfloat16, device=None):
+        """The exchange of this rank in ``group`` (all ranks on one node, NCCL backend)."""
+        from . import _loader
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self = cls(rank=rank, world=world, capacity=capacity, hidden=hidden, top_k=top_k,
+                   local_experts=local_experts, output_dtype=output_dtype, device=device,
+                   group=group)
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            _loader.check(self._lib.gg_peer_export(ctypes.c_void_p(self.base), handle),
+                          "gg_peer_export")
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        bases = []
+        with torch.cuda.device(self.device):
+            for peer, raw in enumerate(handles):
+                if peer == rank:
+                    bases.append(self.base)
+                    continue
+                pointer = ctypes.c_void_p()
+                _loader.check(self._lib.gg_peer_import(ctypes.create_string_buffer(raw, 64),
+                                                       ctypes.byref(pointer)), "gg_peer_import")
+                self._imported.append(pointer.value)
+                bases.append(pointer.value)
+        self._set_peer_bases(bases)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)
+        return self
+
+    @classmethod
+    def local_ranks(cls, world, *, capacity, hidden, top_k, local_experts,
+                    output_dtype=torch.bfloat16, device="cuda"):
+        """``world`` exchanges inside this process on one GPU, addressing each other directly."""
+        ranks = [cls(rank=r, world=world, capacity=capacity, hidden=hidden, top_k=top_k,
+                     local_experts=local_experts, output_dtype=output_dtype, device=device)
+                 for r in range(world)]
+        for exchange in ranks:
+            exchange._set_peer_bases([peer.base for peer in ranks])
+        return ranks
+
+    def close(self):
+        """Unmap the peers' areas and free this rank's.  Call on every rank, after a barrier."""
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for pointer in self._imported:
+                self._lib.gg_peer_release(ctypes.c_void_p(pointer))
+            self._imported = []
+            if self.base:
+                for name in ("recv_x", "recv_scale", "recv_ids", "recv_src", "home_out"):
+                    setattr(self, name, None)
+                self._lib.gg_peer_free(ctypes.c_void_p(self.base))
+                self.base = 0
+
+    # -- the three phases of a step ----------------------------------------------------------
+
+    def dispatch(self, hidden_states, scale_x, topk_ids, token_mask=None):
+        """Plan and send: every token row goes once to every rank that owns one of its experts.
+        Returns this rank's ``counts`` (rows per destination, then the invalid-id count)."""
+        from . import _loader
+        tokens = hidden_states.shape[0]
+        if tokens > self.capacity or hidden_states.shape[1] != self.hidden \
+                or topk_ids.shape[1] != self.top_k:
+            raise ValueError("PeerExchange: token count, hidden size or top-k exceed what the "
+                             "exchange was created for")
+        ids = topk_ids if topk_ids.is_contiguous() else topk_ids.contiguous()
+        mask = None if token_mask is None else token_mask.contiguous()
+        experts = self.local_experts * self.world
+        stream = _loader.stream_pointer(self.device)
+        is_i64 = int(ids.dtype == torch.int64)
+        _loader.check(self._lib.gg_ep_plan(
+            _loader.pointer(ids), is_i64, _loader.pointer(mask), tokens, self.top_k, experts,
+            self.world, self.local_experts, _loader.pointer(self.position),
+            _loader.pointer(self.counts), _loader.pointer(self.home_inverse), stream), "gg_ep_plan")
+        _loader.check(self._lib.gg_ep_dispatch(
+            _loader.pointer(hidden_states), _loader.pointer(scale_x), _loader.pointer(ids), is_i64,
+            _loader.pointer(mask), _loader.pointer(self.position), tokens, self.top_k, experts,
+            self.world, self.local_experts, self.hidden, self.rank, self.capacity,
+            _loader.pointer(self.tables["recv_x"]), _loader.pointer(self.tables["recv_scale"]),
+            _loader.pointer(self.tables["recv_ids"]), _loader.pointer(self.tables["recv_src"]),
+            _loader.pointer(self.flags), stream), "gg_ep_dispatch")
+        return self.counts
+
+    def experts(self, counts_all, w_gate_up, w_down, scale_gate_up, scale_down, gate_up_layout):
+        """Stages 1-3 on the rows that arrived; Down stores each result row into the home
+        rank's ``home_out``.  ``counts_all`` is the all-gathered ``[world, world + 1]`` matrix."""
+        from . import _loader, moe
+        stream = _loader.stream_pointer(self.device)
+        _loader.check(self._lib.gg_ep_row_mask(
+            _loader.pointer(counts_all), self.world, self.rank, self.capacity,
+            _loader.pointer(self.row_mask), stream), "gg_ep_row_mask")
+        routes = moe.prepare_routes(self.recv_ids, self.local_experts, self.row_mask,
+                                    tile_rows=moe.TENSOR_CORE_TILE_ROWS, workspace=self.workspace)
+        qh, sh = moe.gate_up_swiglu_quantize(
+            self.recv_x, self.recv_scale, w_gate_up.transpose(-2, -1), scale_gate_up, routes,
+            output_dtype=self.output_dtype, gate_up_layout=gate_up_layout, workspace=self.workspace)
+        _loader.check(self._lib.gg_ep_row_destination(
+            _loader.pointer(routes.order), _loader.pointer(routes.offsets), self.local_experts,
+            self.top_k, self.capacity, self.world, self.hidden, _loader.OUT_DTYPE[self.output_dtype],
+            _loader.pointer(self.recv_src), _loader.pointer(self.tables["home_out"]),
+            _loader.pointer(self.row_destination), _loader.pointer(self.flags), stream),
+            "gg_ep_row_destination")
+        moe.down_projection(qh, sh, w_down.transpose(-2, -1), scale_down, routes,
+                            output_dtype=self.output_dtype, row_destination=self.row_destination)
+
+    def combine(self, topk_weights):
+        """Top-k weighted sum of this rank's tokens from ``home_out`` (slot order)."""
+        from . import moe
+        tokens = topk_weights.shape[0]
+        routes = SimpleNamespace(inverse=self.home_inverse, tokens=tokens, top_k=self.top_k)
+        return moe.combine(self.home_out[:tokens * self.top_k], topk_weights, routes,
+                           output_dtype=self.output_dtype)
+
+
+def _peer_step(exchange, hidden_states, w_gate_up, w_down, topk_weights, topk_ids, scale_x,
+               scale_gate_up, scale_down, token_mask, gate_up_layout, marks=None):
+    """One expert-parallel FFN through ``exchange`` (see ``PeerExchange``).  ``marks``, a list,
+    receives timing events at the phase boundaries (start, dispatched, counts gathered, experts
+    done, results home, combined)."""
+    world, group = exchange.world, exchange.group
+
+    def mark():
+        if marks is not None:
+            event = torch.cuda.Event(enable_timing=True)
+            event.record()
+            marks.append(event)
+
+    mark()
+    aligned = all(t.data_ptr() % 16 == 0 for t in (hidden_states, w_gate_up, w_down))
+    if not aligned:
+        raise ValueError("the peer exchange needs 16-byte-aligned hidden_states and weights")
+    counts = exchange.dispatch(hidden_states, scale_x, topk_ids, token_mask)
+    mark()
+    # Counts of every rank; the collective also orders "every rank's rows have arrived".
+    if world > 1:
+        dist.all_gather_into_tensor(exchange.counts_all, counts.reshape(1, -1), group=group)
+    else:
+        exchange.counts_all.copy_(counts.reshape(1, -1))
+    mark()
+    exchange.experts(exchange.counts_all, w_gate_up, w_down, scale_gate_up, scale_down,
+                     gate_up_layout)
+    mark()
+    # "All results are home" (and any refused index on any rank) before the combine.
+    if world > 1:
+        dist.all_reduce(exchange.flags, group=group)
+    mark()
+    # Invalid ids and refused indices are read back while the combine runs (not under capture).
+    capturing = torch.cuda.is_current_stream_capturing()
+    host = exchange._host
+    if not capturing:
+        host[:world].copy_(exchange.counts_all[:, world], non_blocking=True)
+        host[world:world + 2].copy_(exchange.flags, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+    out = exchange.combine(topk_weights)
+    mark()
+    if not capturing:
+        event.synchronize()
+        if int(host[world]):
+            exchange.flags.zero_()
+            raise RuntimeError("expert-parallel exchange: a kernel refused an out-of-range row index")
+        if int(host[:world].sum()):
+            raise ValueError("unmasked topk_ids must be in [0, E)")
+    return out
+
+
+def run_local_ranks(exchanges, cases, token_masks=None):
+    """Run one expert-parallel step of every rank of ``PeerExchange.local_ranks`` in this process.
+
+    ``cases[r]`` holds rank r's ``moe_ffn_expert_parallel`` tensors.  The phases run rank by
+    rank (dispatch of all ranks, then the experts of all ranks, then the combines), which is
+    the order the collectives of the multi-process path enforce.  Returns the per-rank outputs.
+    """
+    world = len(exchanges)
+    masks = token_masks or [None] * world
+    counts = [ex.dispatch(case["hidden_states"], case["scale_x"], case["topk_ids"], mask)
+              for ex, case, mask in zip(exchanges, cases, masks)]
+    counts_all = torch.stack(counts).contiguous()
+    if int(counts_all[:, world].sum()):
+        raise ValueError("unmasked topk_ids must be in [0, E)")
+    for ex, case in zip(exchanges, cases):
+        ex.experts(counts_all, case["w_gate_up"], case["w_down"], case["scale_gate_up"],
+                   case["scale_down"], case.get("gate_up_layout", "split"))
+    outputs = [ex.combine(case["topk_weights"]) for ex, case in zip(exchanges, cases)]
+    if any(int(ex.flags[0]) for ex in exchanges):
+        raise RuntimeError("expert-parallel exchange: a kernel refused an out-of-range row index")
+    return outputs
 
 
 def int8_gemm_n_sharded(a, b_local, scale_a, scale_b_local, *, group_size=256,

@@ -123,6 +123,39 @@ def _validate(hidden_states, w_gate_up, w_down, topk_weights, topk_ids,
     return tokens, hidden, intermediate, experts, routes
 
 
+class MoEWorkspace:
+    """Reusable device buffers for the intermediates of ``moe_ffn``.
+
+    Without one every call allocates about ten tensors (routing metadata, the tile list,
+    ``qh``/``sh``, the Gate/Up scratch, the expert outputs); a serving loop passes the same
+    workspace to every call instead and the buffers are only (re)allocated when a shape, dtype
+    or device changes.  A buffer is reused by the next call on the same stream, so the tensors
+    a call got from the workspace are only valid until the next call that uses it; the result
+    of ``moe_ffn`` is never taken from the workspace.  Not thread-safe: one workspace per stream.
+    """
+
+    def __init__(self):
+        self._buffers = {}
+
+    def get(self, name, shape, dtype, device):
+        shape = tuple(int(d) for d in shape)
+        tensor = self._buffers.get(name)
+        if (tensor is None or tuple(tensor.shape) != shape or tensor.dtype != dtype
+                or tensor.device != torch.device(device)):
+            tensor = torch.empty(shape, dtype=dtype, device=device)
+            self._buffers[name] = tensor
+        return tensor
+
+    def nbytes(self):
+        return sum(t.numel() * t.element_size() for t in self._buffers.values())
+
+
+def _buffer(workspace, name, shape, dtype, device):
+    if workspace is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    return workspace.get(name, shape, dtype, device)
+
+
 @dataclass(frozen=True)
 class Routes:
     """GPU-resident routing metadata; valid assignments occupy a sorted prefix.
@@ -149,11 +182,12 @@ class Routes:
     tile_row: torch.Tensor | None = None
 
 
-def prepare_routes(topk_ids, num_experts, token_mask=None, tile_rows=TENSOR_CORE_TILE_ROWS):
+def prepare_routes(topk_ids, num_experts, token_mask=None, tile_rows=TENSOR_CORE_TILE_ROWS,
+                   workspace=None):
     """Stable sort of the assignments by expert plus per-expert metadata, all on the GPU.
 
     Out-of-range ids and masked tokens get key E and sort to the tail.  ``tile_rows=0``
-    skips the row-tile list.
+    skips the row-tile list.  ``token_mask`` may be BOOL or UINT8.
     """
     lib = _loader.library()
     tokens, top_k = topk_ids.shape
@@ -163,35 +197,35 @@ def prepare_routes(topk_ids, num_experts, token_mask=None, tile_rows=TENSOR_CORE
     mask = None
     if token_mask is not None:
         mask = token_mask if token_mask.is_contiguous() else token_mask.contiguous()
-    effective_ids = torch.empty((slots,), dtype=ids.dtype, device=device)
-    order = torch.empty((slots,), dtype=torch.int64, device=device)
-    inverse = torch.empty((slots,), dtype=torch.int32, device=device)
-    counts = torch.empty((num_experts,), dtype=torch.int32, device=device)
-    offsets = torch.empty((num_experts + 1,), dtype=torch.int32, device=device)
-    statistics = torch.empty((3,), dtype=torch.int32, device=device)
+    effective_ids = _buffer(workspace, "effective_ids", (slots,), ids.dtype, device)
+    order = _buffer(workspace, "order", (slots,), torch.int64, device)
+    inverse = _buffer(workspace, "inverse", (slots,), torch.int32, device)
+    counts = _buffer(workspace, "counts", (num_experts,), torch.int32, device)
+    offsets = _buffer(workspace, "offsets", (num_experts + 1,), torch.int32, device)
+    statistics = _buffer(workspace, "statistics", (3,), torch.int32, device)
     workspace_bytes = lib.gg_moe_route_workspace_bytes(tokens, top_k, num_experts)
-    workspace = (torch.empty((workspace_bytes,), dtype=torch.uint8, device=device)
-                 if workspace_bytes else None)
+    scratch = (_buffer(workspace, "route_scratch", (workspace_bytes,), torch.uint8, device)
+               if workspace_bytes else None)
     stream = _loader.stream_pointer(device)
     _loader.check(lib.gg_moe_route(
         _loader.pointer(ids), int(ids.dtype == torch.int64), _loader.pointer(mask),
         tokens, top_k, num_experts, _loader.pointer(effective_ids), _loader.pointer(order),
         _loader.pointer(inverse), _loader.pointer(counts), _loader.pointer(offsets),
-        _loader.pointer(statistics), _loader.pointer(workspace), workspace_bytes, stream),
+        _loader.pointer(statistics), _loader.pointer(scratch), workspace_bytes, stream),
         "gg_moe_route")
     routes = Routes(order, counts, offsets, inverse, effective_ids, statistics,
                     tokens, top_k, num_experts)
-    return prepare_tiles(routes, tile_rows) if tile_rows else routes
+    return prepare_tiles(routes, tile_rows, workspace) if tile_rows else routes
 
 
-def prepare_tiles(routes, tile_rows):
+def prepare_tiles(routes, tile_rows, workspace=None):
     """Return ``routes`` with the row-tile list for tiles of ``tile_rows`` rows added."""
     if routes.tile_rows == tile_rows and routes.tile_expert is not None:
         return routes
     lib = _loader.library()
     device = routes.offsets.device
     capacity = lib.gg_moe_tile_capacity(routes.tokens * routes.top_k, routes.experts, tile_rows)
-    tiles = torch.empty((2, max(capacity, 1)), dtype=torch.int32, device=device)
+    tiles = _buffer(workspace, "tiles", (2, max(capacity, 1)), torch.int32, device)
     _loader.check(lib.gg_moe_tiles(
         _loader.pointer(routes.offsets), routes.experts, tile_rows, capacity,
         _loader.pointer(tiles[0]), _loader.pointer(tiles[1]), _loader.stream_pointer(device)),
@@ -202,7 +236,8 @@ def prepare_tiles(routes, tile_rows):
 
 
 def gate_up_swiglu_quantize(hidden_states, scale_x, w1_linear, scale_gate_up, routes, *,
-                            output_dtype=torch.bfloat16, gate_up_layout="split", row_gather=False):
+                            output_dtype=torch.bfloat16, gate_up_layout="split", row_gather=False,
+                            workspace=None):
     """Stage 2: ``qh[S, I]`` INT8 and ``sh[S, I/256]`` FP32 for the valid sorted slots.
 
     ``w1_linear`` is the contiguous Linear view ``[E, 2I, H]``.  Rows of invalid slots are
@@ -215,12 +250,12 @@ def gate_up_swiglu_quantize(hidden_states, scale_x, w1_linear, scale_gate_up, ro
     intermediate = twice_intermediate // 2
     slots = routes.tokens * routes.top_k
     device = hidden_states.device
-    qh = torch.empty((slots, intermediate), dtype=torch.int8, device=device)
-    sh = torch.empty((slots, intermediate // 256), dtype=torch.float32, device=device)
+    qh = _buffer(workspace, "qh", (slots, intermediate), torch.int8, device)
+    sh = _buffer(workspace, "sh", (slots, intermediate // 256), torch.float32, device)
     with torch.cuda.device(device):
         scratch_bytes = lib.gg_moe_gate_up_scratch_bytes(slots, hidden, intermediate,
                                                          routes.tile_rows, int(row_gather))
-    scratch = torch.empty((max(scratch_bytes, 16),), dtype=torch.uint8, device=device)
+    scratch = _buffer(workspace, "gate_up_scratch", (max(scratch_bytes, 16),), torch.uint8, device)
     _loader.check(lib.gg_moe_gate_up(
         _loader.pointer(hidden_states), _loader.pointer(scale_x), _loader.pointer(w1_linear),
         _loader.pointer(scale_gate_up), _loader.pointer(routes.order),
@@ -233,17 +268,24 @@ def gate_up_swiglu_quantize(hidden_states, scale_x, w1_linear, scale_gate_up, ro
     return qh, sh
 
 
-def down_projection(qh, sh, w2_linear, scale_down, routes, *, output_dtype=torch.bfloat16):
-    """Stage 3: ``expert_output[S, H]`` for the valid sorted slots (``w2_linear`` ``[E, H, I]``)."""
+def down_projection(qh, sh, w2_linear, scale_down, routes, *, output_dtype=torch.bfloat16,
+                    row_destination=None, workspace=None):
+    """Stage 3: ``expert_output[S, H]`` for the valid sorted slots (``w2_linear`` ``[E, H, I]``).
+
+    With ``row_destination`` (INT64 ``[S]`` device addresses, tensor-core path) every row is
+    stored at its own address instead and nothing is returned.
+    """
     lib = _loader.library()
     experts, hidden, intermediate = w2_linear.shape
     slots = routes.tokens * routes.top_k
-    out = torch.empty((slots, hidden), dtype=output_dtype, device=qh.device)
+    out = (_buffer(workspace, "expert_output", (slots, hidden), output_dtype, qh.device)
+           if row_destination is None else None)
     _loader.check(lib.gg_moe_down(
         _loader.pointer(qh), _loader.pointer(sh), _loader.pointer(w2_linear),
         _loader.pointer(scale_down), _loader.pointer(routes.offsets),
         _loader.pointer(routes.tile_expert), _loader.pointer(routes.tile_row),
-        routes.tile_expert.numel(), routes.tile_rows, _loader.pointer(out), slots, experts,
+        routes.tile_expert.numel(), routes.tile_rows, _loader.pointer(out),
+        _loader.pointer(row_destination), slots, experts,
         hidden, intermediate, _loader.OUT_DTYPE[output_dtype],
         _loader.stream_pointer(qh.device)), "gg_moe_down")
     return out
@@ -294,7 +336,7 @@ def _tensor_core_ready(*tensors):
 def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
             scale_x, scale_gate_up, scale_down, group_size=256, activation="swiglu",
             token_mask=None, output_dtype=torch.bfloat16, backend="auto",
-            gate_up_layout="split", variant="auto"):
+            gate_up_layout="split", variant="auto", workspace=None):
     """Run a complete pre-routed INT8 G256 MoE FFN on the current CUDA stream.
 
     ``w_gate_up[E,H,2I]`` and ``w_down[E,I,H]`` are transposed views of contiguous
@@ -312,7 +354,8 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
     ``ValueError`` (the copy overlaps the remaining stages; the call returns or raises once
     routing has run); under CUDA-graph capture that check is skipped.  ``variant`` is
     ``'auto'``, ``'tensor_core'``, ``'tensor_core_gather'`` (the fused Gate/Up kernel fetches
-    token rows by TMA row gathers, no copy in expert order) or ``'cuda_core'``.
+    token rows by TMA row gathers, no copy in expert order) or ``'cuda_core'``.  ``workspace``
+    (a ``MoEWorkspace``) makes repeated calls reuse their intermediate buffers.
     """
     tokens, hidden, intermediate, experts, top_k = _validate(
         hidden_states, w_gate_up, w_down, topk_weights, topk_ids,
@@ -331,7 +374,8 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
             raise ValueError(f"variant='{variant}' requires 16-byte-aligned hidden_states and weights")
         tile_rows = (CUDA_CORE_TILE_ROWS if variant == "cuda_core" or not aligned
                      else TENSOR_CORE_TILE_ROWS)
-        routes = prepare_routes(topk_ids, experts, token_mask, tile_rows=tile_rows)
+        routes = prepare_routes(topk_ids, experts, token_mask, tile_rows=tile_rows,
+                                workspace=workspace)
         # The check for unmasked ids outside [0, E) reads three integers back.  Its copy is
         # started now and awaited after the remaining stages are in the stream (they are safe
         # for any ids: invalid assignments sort to the ignored tail), so the GPU never waits
@@ -340,9 +384,9 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
         qh, sh = gate_up_swiglu_quantize(
             hidden_states, scale_x, w1_linear, scale_gate_up, routes,
             output_dtype=output_dtype, gate_up_layout=gate_up_layout,
-            row_gather=variant == "tensor_core_gather")
+            row_gather=variant == "tensor_core_gather", workspace=workspace)
         expert_output = down_projection(qh, sh, w2_linear, scale_down, routes,
-                                        output_dtype=output_dtype)
+                                        output_dtype=output_dtype, workspace=workspace)
         out = combine(expert_output, topk_weights, routes, output_dtype=output_dtype)
         if readback is not None:
             host, event = readback

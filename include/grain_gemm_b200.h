@@ -220,13 +220,19 @@ int gg_moe_gate_up(const void* x, const void* scale_x, const void* w1, const voi
  * Down projection over the sorted slots: expert_out[S,H] (out_dtype) from q[S,I], s[S,I/256],
  * w2 Linear [E,H,I] contiguous int8, scale_w2 [E,I/256,H].  Rows at or beyond offsets[E] are
  * not written.  tile_rows 128 = tensor cores, 32 = CUDA cores.
+ * row_destination (optional, tensor-core path only): a device array of S 64-bit addresses; row r
+ * is then stored at row_destination[r] (the address of its first element, 16-byte aligned;
+ * 0 = skip the row) instead of expert_out + r * H, and expert_out may be NULL.  The addresses
+ * may point into another GPU's memory mapped on this one: the expert-parallel layer uses this to
+ * return every result row to the token's home rank from inside the GEMM.
  * Replaces the second ragged_gemm (src/grain_gemm/moe.py:305-308) and grain_cutlass_moe_g256
  * (csrc/sm110/int8_g256_moe.cu:287).
  */
 int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_w2,
                 const void* offsets, const void* tile_expert, const void* tile_row,
-                int tile_capacity, int tile_rows, void* expert_out, int assignments, int experts,
-                int hidden, int intermediate, int out_dtype, void* stream);
+                int tile_capacity, int tile_rows, void* expert_out, const void* row_destination,
+                int assignments, int experts, int hidden, int intermediate, int out_dtype,
+                void* stream);
 
 /*
  * out[T,H] = cast( sum_r float(expert_out[inverse[t*R+r]]) * weights[t,r] ), slots with
@@ -235,6 +241,59 @@ int gg_moe_down(const void* q, const void* s, const void* w2, const void* scale_
  */
 int gg_moe_combine(const void* expert_out, const void* weights, const void* inverse, void* out,
                    int tokens, int top_k, int hidden, int out_dtype, void* stream);
+
+/* ---- Expert parallelism over peer memory --------------------------------------------------
+ *
+ * The reference is single-GPU ("one GPU and no communication",
+ * benchmarks/results/thor/moe_ffn_original_x_emc2750.md:26-27); these entry points have no
+ * counterpart there.  Experts are split contiguously over `world` ranks (local_experts each),
+ * tokens are sharded per rank.  Every rank owns a receive area that all ranks of the node can
+ * address (gg_peer_* below), laid out for a token capacity C per rank:
+ *   recv_x [world*C, H] int8, recv_scale [world*C, H/256] fp32, recv_ids [world*C, R] int32,
+ *   recv_src [world*C] int32, home_out [C*R, H] out_dtype.
+ * Rank s writes its rows for rank d at rows [s*C, s*C + n) of d's area, so no offsets have to
+ * be agreed on first; the counts travel afterwards in one all-gather that also orders "all rows
+ * have arrived" before the expert kernels.  All kernels bound every remote index and set *error
+ * instead of touching memory outside the areas.
+ */
+
+/* Per destination rank d and token t: position[t*world + d] = index of t among this rank's rows
+ * for d (token order) or -1; counts[world + 1] = rows per destination, then the number of enabled
+ * ids outside [0, experts); home_inverse[t*R + r] = t*R + r for a valid assignment, else -1 (the
+ * `inverse` gg_moe_combine takes when home_out is indexed by flattened assignment). */
+int gg_ep_plan(const void* ids, int ids_are_i64, const void* mask, int tokens, int top_k,
+               int experts, int world, int local_experts, void* position, void* counts,
+               void* home_inverse, void* stream);
+
+/* Copies every (token, destination) pair's row, scales, per-slot local expert indices
+ * (local_experts = "not on this rank") and home token index into the destination's receive
+ * area.  recv_* are device arrays of `world` 64-bit addresses (valid on this GPU). */
+int gg_ep_dispatch(const void* x, const void* scale_x, const void* ids, int ids_are_i64,
+                   const void* mask, const void* position, int tokens, int top_k, int experts,
+                   int world, int local_experts, int hidden, int rank, int capacity,
+                   const void* recv_x, const void* recv_scale, const void* recv_ids,
+                   const void* recv_src, void* error, void* stream);
+
+/* row_mask[s*C + i] = i < counts_all[s][rank] for the all-gathered counts [world, world + 1]. */
+int gg_ep_row_mask(const void* counts_all, int world, int rank, int capacity, void* row_mask,
+                   void* stream);
+
+/* row_destination[slot] for gg_moe_down: the row of assignment (received token m, slot r) goes
+ * to home_out[m / C] + ((recv_src[m] * R + r) * H) elements; 0 beyond the valid prefix. */
+int gg_ep_row_destination(const void* order, const void* offsets, int experts, int top_k,
+                          int capacity, int world, int hidden, int out_dtype, const void* recv_src,
+                          const void* home_out, void* row_destination, void* error, void* stream);
+
+/* Device memory that other processes of the node can map (CUDA IPC; set-up time only: these
+ * allocate, map or free and are not meant for the hot path).  gg_peer_alloc returns zeroed
+ * memory from cudaMalloc; gg_peer_export fills a 64-byte handle another process passes to
+ * gg_peer_import, which maps the allocation (peer access is enabled lazily) and returns an
+ * address valid in that process; gg_peer_release unmaps, gg_peer_free frees. */
+int gg_peer_alloc(size_t bytes, void** pointer);
+int gg_peer_free(void* pointer);
+int gg_peer_export(void* pointer, void* handle64);
+int gg_peer_import(const void* handle64, void** pointer);
+int gg_peer_release(void* pointer);
 
 /*
  * Reads (and clears) the device status word that kernels set when one of their bounded
