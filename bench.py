@@ -60,6 +60,11 @@ def parse():
     parser.add_argument("--variant", default="auto")
     parser.add_argument("--skip-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
+    parser.add_argument("--sweep", action="store_true",
+                        help="measure every tensor-core variant over the shape grid and write the "
+                             "shape -> variant table the package loads (one GPU)")
+    parser.add_argument("--sweep-output", default=str(ROOT / "grain_gemm_b200" / "configs"
+                                                      / "b200_sm100_variants.json"))
     parser.add_argument("--skip-sustained", action="store_true")
     parser.add_argument("--skip-library-probe", action="store_true")
     return parser.parse_args()
@@ -459,6 +464,65 @@ def run_moe(args, rank, world, device, barrier):
     return report
 
 
+SWEEP_M = [1, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192]
+SWEEP_NK = [(8192, 8192), (4096, 4096), (4096, 7168), (7168, 2048), (28672, 4096), (4096, 14336)]
+SWEEP_VARIANTS = ["tc_n256", "tc_n128", "tc_n64", "tc_pair_n256", "tc_pair_n128", "tc_splitk"]
+
+
+def run_sweep(args, device):
+    """Times every tensor-core variant on M x (N, K) x G and writes, per (G, N, K), the fastest
+    variant for each M bucket (the table ``get_kernel_config`` / ``int8_gemm`` consult)."""
+    from grain_gemm_b200 import _loader, gemm
+
+    lib = _loader.library()
+    shapes, timings = {}, {}
+    for g in (256, 128, 64, 32):
+        for n, k in SWEEP_NK:
+            rows = []
+            for m in SWEEP_M:
+                a, w, scale_a, scale_b = make_gemm_inputs(m, n, k, g, 7, device)
+                out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+                best = None
+                for variant in SWEEP_VARIANTS:
+                    if variant == "tc_splitk" and not lib.gg_int8_gemm_workspace_bytes(m, n, k, g):
+                        continue
+                    if variant.startswith("tc_pair") and m <= 128:
+                        continue
+                    try:
+                        for _ in range(3):
+                            gemm.launch(a, w.t(), scale_a, scale_b, out, g, variant)
+                    except RuntimeError:
+                        continue
+                    torch.cuda.synchronize()
+                    start, stop = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+                    iterations = 20 if m * n * k < 2 ** 36 else 5
+                    start.record()
+                    for _ in range(iterations):
+                        gemm.launch(a, w.t(), scale_a, scale_b, out, g, variant)
+                    stop.record()
+                    torch.cuda.synchronize()
+                    microseconds = start.elapsed_time(stop) / iterations * 1e3
+                    timings[f"{g}:{n}:{k}:{m}:{variant}"] = round(microseconds, 2)
+                    if best is None or microseconds < best[0]:
+                        best = (microseconds, variant)
+                if best is not None:
+                    if rows and rows[-1][1] == best[1]:
+                        rows[-1][0] = m
+                    else:
+                        rows.append([m, best[1]])
+                del a, w, scale_a, scale_b, out
+            if rows:
+                rows[-1][0] = 2 ** 31 - 1
+                shapes[f"{g}:{n}:{k}"] = rows
+    table = {"device": torch.cuda.get_device_name(device), "measured_with": "bench.py --sweep",
+             "key": "G:N:K -> [[largest M, variant], ...] in ascending M", "shapes": shapes,
+             "microseconds": timings}
+    output = Path(args.sweep_output)
+    output.parent.mkdir(parents=True, exist_ok=True)
+    output.write_text(json.dumps(table, indent=1) + "\n")
+    print(json.dumps({"sweep": str(output), "shapes": len(shapes), "timings": len(timings)}))
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -481,6 +545,12 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.sweep:
+        if world != 1:
+            raise SystemExit("--sweep runs on one GPU")
+        run_sweep(args, device)
+        return
 
     if args.only_moe:
         report = run_moe(args, rank, world, device, barrier)

@@ -8,9 +8,41 @@ C ABI of ``libgrain_b200.so``.  There is no Triton path and no CPU fallback.
 
 from __future__ import annotations
 
+import json
+from functools import lru_cache
+from pathlib import Path
+
 import torch
 
 from . import _loader
+
+_TABLE = Path(__file__).resolve().parent / "configs" / "b200_sm100_variants.json"
+
+
+@lru_cache(maxsize=1)
+def _variant_table():
+    """Measured shape -> variant table (``bench.py --sweep`` writes it), like the reference's
+    per-GPU dispatch tables (``src/grain_gemm/gemm.py:53-69``, ``kernels/configs/*.json``).
+
+    Keys are ``"G:N:K"``; each entry lists ``[m_upper_bound, variant]`` pairs in ascending
+    order of M.  A missing file or shape leaves the choice to the library's own rule."""
+    try:
+        data = json.loads(_TABLE.read_text())
+    except (OSError, ValueError):
+        return {}
+    return {key: [(int(bound), str(name)) for bound, name in rows]
+            for key, rows in data.get("shapes", {}).items()}
+
+
+def _table_variant(m, n, k, group_size):
+    """Variant the measured table names for this shape, or None."""
+    rows = _variant_table().get(f"{group_size}:{n}:{k}")
+    if not rows:
+        return None
+    for bound, name in rows:
+        if m <= bound:
+            return name
+    return rows[-1][1]
 
 _BACKENDS = ("auto", "cuda")
 _FOREIGN_BACKENDS = ("triton", "cutlass")
@@ -118,10 +150,14 @@ def get_kernel_config(a, b, *, group_size=256, output_dtype=torch.bfloat16,
         else:
             variant = _select(a, b, None, group_size, output_dtype)
     name = _loader.VARIANT_NAMES[variant]
+    policy = "sm100_native"
+    tabled = _table_variant(m, n, k, group_size)
+    if tabled is not None and name.startswith("tc"):
+        name, policy = tabled, "sm100_table"
     pair = name.startswith("tc_pair")
     block_n = (256 if name == "tc_splitk" else int(name.split("_n", 1)[1].split("_")[0])
                if name.startswith("tc") else 32)
-    return dict(policy="sm100_native", compute_capability=list(capability), backend="cuda",
+    return dict(policy=policy, compute_capability=list(capability), backend="cuda",
                 variant=name, block_m=(256 if pair else 128) if name.startswith("tc") else 32,
                 block_n=block_n, cta_group=2 if pair else 1,
                 tensor_cores=name.startswith("tc"), repacked_a=repack_a, repacked_b=repack_b)
@@ -156,12 +192,23 @@ def _tensor_core_operands(a, b):
     return a, b
 
 
+def _tc_ready(a, b):
+    """Operands the tensor-core variants accept (K contiguous, 16-byte aligned rows)."""
+    a_sm, a_sk, b_sk, b_sn = _operand_strides(a, b)
+    k = a.shape[1]
+    return (a_sk == 1 and b_sk == 1 and a_sm % 16 == 0 and b_sn % 16 == 0 and a_sm >= k
+            and b_sn >= k and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
+
+
 def launch(a, b, scale_a, scale_b, out, group_size, variant="auto"):
     """Launch the GEMM on torch's current stream (arguments already validated)."""
     m, k = a.shape
     n = b.shape[1]
     if variant == "auto":
         a, b = _tensor_core_operands(a, b)
+        tabled = _table_variant(m, n, k, group_size)
+        if tabled is not None and _tc_ready(a, b):
+            variant = tabled
     lib = _loader.library()
     workspace, workspace_bytes = None, 0
     if variant in ("auto", "tc_splitk"):

@@ -209,7 +209,9 @@ def test_split_k_for_skinny_m_is_bit_exact(gg, m, n, k, g):
         expected = oracle.int8_gemm(*tensors, g, dtype)
         assert torch.equal(run(gg, tensors, g, dtype, "tc_splitk"), expected)
     a, b, _, _ = (t.cuda() for t in tensors)
-    assert gg.get_kernel_config(a, b, group_size=g)["variant"] == "tc_splitk"
+    config = gg.get_kernel_config(a, b, group_size=g)
+    # The library's own rule splits K for these shapes; a measured table entry may overrule it.
+    assert config["variant"] == "tc_splitk" or config["policy"] == "sm100_table"
 
 
 @pytest.mark.parametrize("m", [1, 16, 128])
@@ -283,7 +285,7 @@ def test_zero_sized_and_config_description(gg):
     assert out.shape == (0, 8) and out.dtype == torch.bfloat16
     a, b, _, _ = (t.cuda() for t in linear_case(8192, 8192, 512, 256, seed=1))
     config = gg.get_kernel_config(a, b, group_size=256)
-    assert config["backend"] == "cuda" and config["policy"] == "sm100_native"
+    assert config["backend"] == "cuda" and config["policy"] in ("sm100_native", "sm100_table")
     assert config["compute_capability"] == [10, 0] and config["tensor_cores"]
     config = gg.get_kernel_config(a, b.contiguous(), group_size=256)
     assert config["tensor_cores"] and config["repacked_b"] and not config["repacked_a"]
