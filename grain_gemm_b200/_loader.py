@@ -46,6 +46,7 @@ _SIGNATURES = {
     "gg_moe_tile_capacity": (_INT, [_INT] * 3),
     "gg_moe_tiles": (_INT, [_VOID, _INT, _INT, _INT, _VOID, _VOID, _VOID]),
     "gg_moe_topk": (_INT, [_VOID, _INT, _INT, _INT, _INT, _VOID, _VOID, _INT, _VOID]),
+    "gg_moe_route_topk": (_INT, [_VOID, _INT, _VOID, _INT, _INT, _INT, _VOID, _VOID, _INT] + [_VOID] * 7),
     "gg_quantize_rows": (_INT, [_VOID, _INT, _LL, _INT, _INT, _VOID, _VOID, _VOID]),
     "gg_moe_silu_table": (_INT, [_VOID, _INT, _VOID]),
     "gg_moe_gate_up_scratch_bytes": (_SIZE, [_INT] * 5),

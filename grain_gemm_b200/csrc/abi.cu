@@ -939,6 +939,44 @@ int gg_moe_topk(const void* logits, int in_dtype, int tokens, int experts, int t
   return static_cast<int>(cudaGetLastError());
 }
 
+int gg_moe_route_topk(const void* logits, int in_dtype, const void* mask, int tokens, int experts,
+                      int top_k, void* weights, void* ids, int ids_are_i64, void* effective_ids,
+                      void* order, void* inverse, void* counts, void* offsets, void* statistics,
+                      void* stream_ptr) {
+  const long long slots = static_cast<long long>(tokens) * top_k;
+  if (tokens <= 0 || experts <= 0 || experts > 1024 || top_k <= 0 || top_k > experts ||
+      slots > gg::kRouteChunk ||
+      (in_dtype != GG_OUT_FP32 && in_dtype != GG_OUT_BF16 && in_dtype != GG_OUT_FP16) || !logits ||
+      !weights || !ids || !effective_ids || !order || !inverse || !counts || !offsets || !statistics) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  gg::RouteParams p = {};
+  p.ids = ids;
+  p.ids_are_i64 = ids_are_i64;
+  p.mask = static_cast<const uint8_t*>(mask);
+  p.tokens = tokens; p.top_k = top_k; p.experts = experts;
+  p.effective_ids = effective_ids;
+  p.order = static_cast<long long*>(order);
+  p.inverse = static_cast<int*>(inverse);
+  p.counts = static_cast<int*>(counts);
+  p.offsets = static_cast<int*>(offsets);
+  p.statistics = static_cast<int*>(statistics);
+  const size_t smem = static_cast<size_t>(experts + 2) * sizeof(int);
+  float* w = static_cast<float*>(weights);
+  if (in_dtype == GG_OUT_FP32) {
+    gg::route_topk_single_kernel<float><<<1, gg::kRouteChunk, smem, stream>>>(
+        static_cast<const float*>(logits), w, p);
+  } else if (in_dtype == GG_OUT_BF16) {
+    gg::route_topk_single_kernel<__nv_bfloat16><<<1, gg::kRouteChunk, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(logits), w, p);
+  } else {
+    gg::route_topk_single_kernel<__half><<<1, gg::kRouteChunk, smem, stream>>>(
+        static_cast<const __half*>(logits), w, p);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
 int gg_quantize_rows(const void* x, int in_dtype, long long rows, int width, int group_size,
                      void* q, void* s, void* stream_ptr) {
   const bool group_ok = group_size == 32 || group_size == 64 || group_size == 128 || group_size == 256;

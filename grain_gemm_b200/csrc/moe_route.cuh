@@ -91,8 +91,7 @@ __device__ __forceinline__ void route_finish_totals(const RouteParams& p, int* b
 }
 
 // Whole routing problem in one CTA (S <= 1024): keys, histogram, scan and placement.
-__global__ void __launch_bounds__(kRouteChunk) route_single_kernel(const RouteParams p) {
-  extern __shared__ int bins[];  // [E + 2]; the last entry counts invalid ids
+__device__ __forceinline__ void route_single_body(const RouteParams& p, int* bins) {
   const long long slots = static_cast<long long>(p.tokens) * p.top_k;
   for (int i = threadIdx.x; i < p.experts + 2; i += blockDim.x) bins[i] = 0;
   __syncthreads();
@@ -109,6 +108,11 @@ __global__ void __launch_bounds__(kRouteChunk) route_single_kernel(const RoutePa
   if (threadIdx.x == 0) route_finish_totals(p, bins, bins[p.experts + 1]);
   __syncthreads();
   route_place_chunk(p, s, present, key, bins);
+}
+
+__global__ void __launch_bounds__(kRouteChunk) route_single_kernel(const RouteParams p) {
+  extern __shared__ int bins[];  // [E + 2]; the last entry counts invalid ids
+  route_single_body(p, bins);
 }
 
 __global__ void __launch_bounds__(kRouteChunk) route_histogram_kernel(const RouteParams p) {
@@ -293,13 +297,10 @@ __device__ __forceinline__ int quantize_value_by_fma(float h, float scale, float
 // it to the caller: benchmarks/bench_moe_ffn.py:283-285, docs/moe_ffn.md:5-7).  One warp per
 // token; expert e lives in lane e % 32, slot e / 32 (E <= 1024).  Logits must be finite.
 template <typename InT>
-__global__ void __launch_bounds__(256)
-router_topk_kernel(const InT* __restrict__ logits, int tokens, int experts, int top_k,
-                   float* __restrict__ weights, void* __restrict__ ids, int ids_are_i64) {
-  const int lane = threadIdx.x & 31;
-  const int token = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (token >= tokens) return;
-  const InT* row = logits + static_cast<long long>(token) * experts;
+__device__ __forceinline__ void router_topk_token(const InT* __restrict__ row, int experts, int top_k,
+                                                  float* __restrict__ weights,
+                                                  void* __restrict__ ids, int ids_are_i64,
+                                                  long long token, int lane) {
   constexpr float kLowest = -3.402823466e+38f;
   float value[32];
 #pragma unroll
@@ -345,7 +346,7 @@ router_topk_kernel(const InT* __restrict__ logits, int tokens, int experts, int 
       // Flush up to 32 selections; weights are divided by the final total below.
       const int base = r & ~31;
       if (lane <= (r & 31)) {
-        const long long slot = static_cast<long long>(token) * top_k + base + lane;
+        const long long slot = token * top_k + base + lane;
         weights[slot] = mine;
         if (ids_are_i64) reinterpret_cast<long long*>(ids)[slot] = mine_id;
         else reinterpret_cast<int*>(ids)[slot] = mine_id;
@@ -354,9 +355,39 @@ router_topk_kernel(const InT* __restrict__ logits, int tokens, int experts, int 
   }
   __syncwarp();
   for (int r = lane; r < top_k; r += 32) {
-    const long long slot = static_cast<long long>(token) * top_k + r;
+    const long long slot = token * top_k + r;
     weights[slot] = __fdiv_rn(weights[slot], total);
   }
+}
+
+template <typename InT>
+__global__ void __launch_bounds__(256)
+router_topk_kernel(const InT* __restrict__ logits, int tokens, int experts, int top_k,
+                   float* __restrict__ weights, void* __restrict__ ids, int ids_are_i64) {
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (token >= tokens) return;
+  router_topk_token(logits + static_cast<long long>(token) * experts, experts, top_k, weights, ids,
+                    ids_are_i64, token, lane);
+}
+
+// Router front-end and routing in one launch for decode-sized problems (T * R <= 1024,
+// E <= 1024): the warps of one CTA select every token's experts, and the same CTA then
+// sorts the assignments it has just written (row N3 of the next rows: the ids never leave the
+// SM's caches between top-k and the histogram).  p.ids is the id output of the first half and
+// the input of the second.
+template <typename InT>
+__global__ void __launch_bounds__(kRouteChunk)
+route_topk_single_kernel(const InT* __restrict__ logits, float* __restrict__ weights,
+                         const RouteParams p) {
+  extern __shared__ int bins[];  // [E + 2]
+  const int lane = threadIdx.x & 31;
+  for (int token = threadIdx.x >> 5; token < p.tokens; token += kRouteChunk / 32) {
+    router_topk_token(logits + static_cast<long long>(token) * p.experts, p.experts, p.top_k,
+                      weights, const_cast<void*>(p.ids), p.ids_are_i64, token, lane);
+  }
+  __syncthreads();   // the ids written above are read back by other warps of this CTA
+  route_single_body(p, bins);
 }
 
 // Entry quantiser: symmetric per-row, per-K-group INT8 quantisation of floating rows,

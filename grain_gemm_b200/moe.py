@@ -336,7 +336,7 @@ def _tensor_core_ready(*tensors):
 def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
             scale_x, scale_gate_up, scale_down, group_size=256, activation="swiglu",
             token_mask=None, output_dtype=torch.bfloat16, backend="auto",
-            gate_up_layout="split", variant="auto", workspace=None):
+            gate_up_layout="split", variant="auto", workspace=None, routes=None):
     """Run a complete pre-routed INT8 G256 MoE FFN on the current CUDA stream.
 
     ``w_gate_up[E,H,2I]`` and ``w_down[E,I,H]`` are transposed views of contiguous
@@ -355,7 +355,8 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
     routing has run); under CUDA-graph capture that check is skipped.  ``variant`` is
     ``'auto'``, ``'tensor_core'``, ``'tensor_core_gather'`` (the fused Gate/Up kernel fetches
     token rows by TMA row gathers, no copy in expert order) or ``'cuda_core'``.  ``workspace``
-    (a ``MoEWorkspace``) makes repeated calls reuse their intermediate buffers.
+    (a ``MoEWorkspace``) makes repeated calls reuse their intermediate buffers.  ``routes``
+    (from ``prepare_routes`` or ``route_topk_routes`` on the same ids and mask) skips stage 1.
     """
     tokens, hidden, intermediate, experts, top_k = _validate(
         hidden_states, w_gate_up, w_down, topk_weights, topk_ids,
@@ -374,8 +375,13 @@ def moe_ffn(hidden_states, w_gate_up, w_down, topk_weights, topk_ids, *,
             raise ValueError(f"variant='{variant}' requires 16-byte-aligned hidden_states and weights")
         tile_rows = (CUDA_CORE_TILE_ROWS if variant == "cuda_core" or not aligned
                      else TENSOR_CORE_TILE_ROWS)
-        routes = prepare_routes(topk_ids, experts, token_mask, tile_rows=tile_rows,
-                                workspace=workspace)
+        if routes is None:
+            routes = prepare_routes(topk_ids, experts, token_mask, tile_rows=tile_rows,
+                                    workspace=workspace)
+        else:
+            if (routes.tokens, routes.top_k, routes.experts) != (tokens, top_k, experts):
+                raise ValueError("routes were prepared for other topk_ids or another expert count")
+            routes = prepare_tiles(routes, tile_rows, workspace)
         # The check for unmasked ids outside [0, E) reads three integers back.  Its copy is
         # started now and awaited after the remaining stages are in the stream (they are safe
         # for any ids: invalid assignments sort to the ignored tail), so the GPU never waits

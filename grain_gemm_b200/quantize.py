@@ -87,6 +87,50 @@ def route_topk(logits, top_k, *, ids_dtype=torch.int64):
     return weights, ids
 
 
+def route_topk_routes(logits, top_k, *, token_mask=None, ids_dtype=torch.int64, tile_rows=128):
+    """``route_topk`` and ``moe.prepare_routes`` together: ``(topk_weights, topk_ids, routes)``.
+
+    For decode-sized problems (``T * top_k <= 1024``) both steps run in ONE kernel launch
+    (``gg_moe_route_topk``: the CTA that selects the experts sorts the assignments it has just
+    written); larger problems make the two calls.  Pass ``routes`` on to
+    ``moe_ffn(..., routes=routes)`` to skip its own routing.  Results are identical either way.
+    """
+    from . import moe
+    if not isinstance(logits, torch.Tensor) or logits.dim() != 2:
+        raise ValueError("logits must be a [T, E] tensor")
+    tokens, experts = logits.shape
+    fused = (0 < tokens * top_k <= 1024 and 0 < top_k <= experts <= 1024
+             and logits.dtype in _loader.OUT_DTYPE and logits.device.type == "cuda"
+             and logits.is_contiguous() and ids_dtype in (torch.int32, torch.int64))
+    if not fused:
+        weights, ids = route_topk(logits, top_k, ids_dtype=ids_dtype)
+        return weights, ids, moe.prepare_routes(ids, experts, token_mask, tile_rows=tile_rows)
+    device = logits.device
+    slots = tokens * top_k
+    weights = torch.empty((tokens, top_k), dtype=torch.float32, device=device)
+    ids = torch.empty((tokens, top_k), dtype=ids_dtype, device=device)
+    effective_ids = torch.empty((slots,), dtype=ids_dtype, device=device)
+    order = torch.empty((slots,), dtype=torch.int64, device=device)
+    inverse = torch.empty((slots,), dtype=torch.int32, device=device)
+    counts = torch.empty((experts,), dtype=torch.int32, device=device)
+    offsets = torch.empty((experts + 1,), dtype=torch.int32, device=device)
+    statistics = torch.empty((3,), dtype=torch.int32, device=device)
+    mask = None if token_mask is None else token_mask.contiguous()
+    lib = _loader.library()
+    with torch.cuda.device(device):
+        _loader.check(lib.gg_moe_route_topk(
+            _loader.pointer(logits), _loader.OUT_DTYPE[logits.dtype], _loader.pointer(mask), tokens,
+            experts, top_k, _loader.pointer(weights), _loader.pointer(ids),
+            int(ids_dtype == torch.int64), _loader.pointer(effective_ids), _loader.pointer(order),
+            _loader.pointer(inverse), _loader.pointer(counts), _loader.pointer(offsets),
+            _loader.pointer(statistics), _loader.stream_pointer(device)), "gg_moe_route_topk")
+        routes = moe.Routes(order, counts, offsets, inverse, effective_ids, statistics, tokens,
+                            top_k, experts)
+        if tile_rows:
+            routes = moe.prepare_tiles(routes, tile_rows)
+    return weights, ids, routes
+
+
 def prepare_weight(linear_weight, group_size=256):
     """Quantise Linear-format weights ``[E, N, K]`` (or ``[N, K]``) once, outside forward.
 

@@ -165,6 +165,17 @@ int gg_moe_topk(const void* logits, int in_dtype, int tokens, int experts, int t
                 void* ids, int ids_are_i64, void* stream);
 
 /*
+ * gg_moe_topk followed by gg_moe_route in ONE launch, for decode-sized problems
+ * (tokens * top_k <= 1024, experts <= 1024; anything larger returns cudaErrorInvalidValue and the
+ * caller makes the two calls): the CTA that selects the experts sorts the assignments it has
+ * just written.  Arguments and results as for the two entry points (ids is an output here).
+ */
+int gg_moe_route_topk(const void* logits, int in_dtype, const void* mask, int tokens, int experts,
+                      int top_k, void* weights, void* ids, int ids_are_i64, void* effective_ids,
+                      void* order, void* inverse, void* counts, void* offsets, void* statistics,
+                      void* stream);
+
+/*
  * Entry quantiser (the step before both paths): x[rows, width] of dtype in_dtype (GG_OUT_FP32,
  * GG_OUT_BF16 or GG_OUT_FP16 name the element type), contiguous, width a multiple of 256,
  * 16-byte aligned; writes q[rows, width] int8 and s[rows, width/group_size] fp32 with

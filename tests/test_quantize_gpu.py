@@ -121,3 +121,39 @@ def test_router_output_feeds_moe_ffn(quantize):
     expected = oracle.moe_ffn(x.cpu(), w1.cpu(), w2.cpu(), weights.cpu(), ids.cpu(), scale_x=sx.cpu(),
                               scale_gate_up=s1.cpu(), scale_down=s2.cpu())
     torch.testing.assert_close(out.float().cpu(), expected.float(), rtol=1e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize("tokens,experts,top_k", [(16, 8, 2), (128, 128, 8), (100, 1000, 10),
+                                                  (1024, 64, 1), (512, 128, 8)])
+def test_router_and_routing_in_one_launch(quantize, tokens, experts, top_k):
+    """Decode-sized problems run top-k and the routing sort in one kernel; ids, weights and all
+    routing metadata equal those of the two separate calls (the last case is too large for the
+    fused kernel and takes the two calls inside the helper)."""
+    from grain_gemm_b200 import moe
+    gen = torch.Generator().manual_seed(tokens + experts)
+    logits = (torch.randn((tokens, experts), generator=gen) * 2).cuda()
+    mask = (torch.rand((tokens,), generator=gen) > 0.2).cuda()
+    for dtype in (torch.int64, torch.int32):
+        weights, ids, routes = quantize.route_topk_routes(logits, top_k, token_mask=mask,
+                                                          ids_dtype=dtype)
+        expected_weights, expected_ids = quantize.route_topk(logits, top_k, ids_dtype=dtype)
+        expected = moe.prepare_routes(expected_ids, experts, mask)
+        assert torch.equal(ids, expected_ids) and torch.equal(weights, expected_weights)
+        for field in ("order", "inverse", "counts", "offsets", "effective_ids", "statistics",
+                      "tile_expert", "tile_row"):
+            assert torch.equal(getattr(routes, field), getattr(expected, field)), field
+
+
+def test_moe_ffn_accepts_prepared_routes(quantize):
+    from grain_gemm_b200 import moe_ffn
+    gen = torch.Generator().manual_seed(22)
+    tokens, hidden, inter, experts, top_k = 60, 512, 256, 6, 2
+    x, sx = quantize.quantize_rows(torch.randn((tokens, hidden), generator=gen).cuda())
+    w1, s1 = quantize.prepare_weight((torch.randn((experts, 2 * inter, hidden), generator=gen) / hidden ** 0.5).cuda())
+    w2, s2 = quantize.prepare_weight((torch.randn((experts, hidden, inter), generator=gen) / inter ** 0.5).cuda())
+    logits = torch.randn((tokens, experts), generator=gen).cuda()
+    weights, ids, routes = quantize.route_topk_routes(logits, top_k)
+    plain = moe_ffn(x, w1, w2, weights, ids, scale_x=sx, scale_gate_up=s1, scale_down=s2)
+    routed = moe_ffn(x, w1, w2, weights, ids, scale_x=sx, scale_gate_up=s1, scale_down=s2,
+                     routes=routes)
+    assert torch.equal(plain, routed)
