@@ -311,11 +311,21 @@ def run_moe(args, rank, world, device, barrier):
     case = bench_moe.make_case(name, device, rank=rank, world=world)
     local_tokens = config["tokens"] // world
     workspace = moe.MoEWorkspace()
-    exchange = None
+    exchange, exchange_error = None, None
     if world > 1:
-        exchange = distributed.PeerExchange.create(
-            dist.group.WORLD, capacity=local_tokens, hidden=config["hidden"],
-            top_k=config["top_k"], local_experts=config["experts"] // world)
+        # Peer mappings need CUDA IPC between the ranks' processes; where a host does not allow
+        # it, every rank falls back to the NCCL all-to-all path together and the line says so.
+        try:
+            exchange = distributed.PeerExchange.create(
+                dist.group.WORLD, capacity=local_tokens, hidden=config["hidden"],
+                top_k=config["top_k"], local_experts=config["experts"] // world)
+        except Exception as error:   # noqa: BLE001 - reported in the JSON line
+            exchange_error = f"{type(error).__name__}: {error}"[:200]
+        usable = torch.tensor([int(exchange is not None)], device=device)
+        dist.all_reduce(usable, op=dist.ReduceOp.MIN)
+        if not int(usable.item()) and exchange is not None:
+            exchange.close()
+            exchange = None
 
     def step(tensors, marks=None, nccl=False):
         if world == 1:
@@ -346,7 +356,7 @@ def run_moe(args, rank, world, device, barrier):
 
     # Phase times of the expert-parallel step (rank 0's events; no extra synchronisation).
     phases = None
-    if world > 1:
+    if exchange is not None:
         names = ["plan_and_dispatch", "count_all_gather", "local_experts", "results_home_all_reduce",
                  "combine"]
         totals = [0.0] * len(names)
@@ -370,16 +380,21 @@ def run_moe(args, rank, world, device, barrier):
             whole = bench_moe.make_case("ep_check", device)
             rows = slice(rank * (768 // world), (rank + 1) * (768 // world))
             single = moe.moe_ffn(**whole)[rows]
-            check = distributed.PeerExchange.create(dist.group.WORLD, capacity=768 // world,
-                                                    hidden=1024, top_k=4, local_experts=16 // world)
-            via_peers = distributed.moe_ffn_expert_parallel(**small, num_experts=16, exchange=check)
+            check = None
+            if exchange is not None:
+                check = distributed.PeerExchange.create(dist.group.WORLD, capacity=768 // world,
+                                                        hidden=1024, top_k=4,
+                                                        local_experts=16 // world)
             via_nccl = distributed.moe_ffn_expert_parallel(**small, num_experts=16)
+            via_peers = via_nccl if check is None else distributed.moe_ffn_expert_parallel(
+                **small, num_experts=16, exchange=check)
             same = torch.tensor([int(torch.equal(via_peers, single) and torch.equal(via_nccl, single))],
                                 device=device)
             dist.all_reduce(same, op=dist.ReduceOp.MIN)
             identical = bool(same.item())
             barrier()
-            check.close()
+            if check is not None:
+                check.close()
 
     # End to end: the per-token inputs come from pinned host memory, the result goes back.
     token_names = ("hidden_states", "scale_x", "topk_weights", "topk_ids")
@@ -406,6 +421,7 @@ def run_moe(args, rank, world, device, barrier):
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         cpu = cpu_moe_sample(name, case, device)
+    exchange_used = exchange is not None
     if exchange is not None:
         barrier()
         exchange.close()
@@ -439,7 +455,8 @@ def run_moe(args, rank, world, device, barrier):
         "n_gpus": world, "steps": steps, "ms_per_step": ms, "scaling": "strong",
         "useful_tops": useful_tops,
         "config": {"workload": f"moe_{name}", **{k: v for k, v in config.items()},
-                   "parallelism": "single" if world == 1 else f"ep{world}_peer_memory_exchange"},
+                   "parallelism": "single" if world == 1 else
+                   (f"ep{world}_peer_memory_exchange" if exchange_used else f"ep{world}_nccl_all_to_all")},
         "roofline": roofline, "clocks": sampler.summary(),
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": world * sum(t.numel() * t.element_size() for t in host.values()),
@@ -451,6 +468,8 @@ def run_moe(args, rank, world, device, barrier):
     }
     if stages is not None:
         report["stage_ms"] = stages
+    if exchange_error is not None:
+        report["peer_exchange_unavailable"] = exchange_error
     if phases is not None:
         report["phases_ms"] = phases
         report["nccl_all_to_all_ms"] = nccl_ms
