@@ -39,7 +39,7 @@ sys.path.insert(0, str(ROOT))
 
 # DRAM traffic of one launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum
 # from the ncu capture summarised in profiles/); None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"gemm_g256_m8192_n8192_k8192_bf16": 365767168}
+NCU_TRAFFIC_BYTES = {"gemm_g256_m8192_n8192_k8192_bf16": 250927360 + 119968000}
 
 
 def parse():
@@ -262,7 +262,8 @@ class HostPipeline:
 # Per-launch DRAM traffic of the two MoE GEMM stages on the large configuration, scaled from the
 # ncu captures of one rank's share (T = 2048, 32 experts; profiles/): traffic there is weight
 # dominated and grows with the number of experts touched, i.e. by 8 for all 256 experts.
-MOE_NCU_TRAFFIC_BYTES = {"large": {"gate_up": 8 * 1.15e9, "down": 8 * 0.60e9}}
+MOE_NCU_TRAFFIC_BYTES = {"large": {"gate_up": 8 * (1.145490e9 + 34.562816e6),
+                                   "down": 8 * (539.494144e6 + 215.468032e6)}}
 
 
 def cpu_moe_sample(name, case, device, experts_sampled=4):
