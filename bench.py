@@ -67,7 +67,68 @@ def parse():
                                                       / "b200_sm100_variants.json"))
     parser.add_argument("--skip-sustained", action="store_true")
     parser.add_argument("--skip-library-probe", action="store_true")
+    parser.add_argument("--skip-reference-gpu", action="store_true",
+                        help="do not time the reference's own Triton path on this GPU (context)")
     return parser.parse_args()
+
+
+def reference_gpu_module():
+    try:
+        from oracle import make_ref
+        return make_ref.load()
+    except Exception:  # the reference is optional context
+        return None
+
+
+def time_calls(call, start, stop, warmup=3, steps=5):
+    for _ in range(warmup):
+        call()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        call()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / steps
+
+
+def reference_gpu_triton_gemm(a, b, scale_a, scale_b, g, start, stop):
+    """The reference's int8_gemm(backend="triton") on the bench's own operands."""
+    module = reference_gpu_module()
+    if module is None:
+        return None
+    m, k = a.shape
+    n = b.shape[1]
+    try:
+        ms = time_calls(lambda: module.int8_gemm(a, b, scale_a, scale_b, group_size=g,
+                                                 output_dtype=torch.bfloat16, backend="triton"),
+                        start, stop)
+    except Exception as error:
+        return {"gemm_unavailable": str(error).splitlines()[0][:200]}
+    return {"gemm_ms_per_step": ms, "gemm_value": 2.0 * m * n * k / (ms * 1e-3) / 1e12,
+            "gemm_unit": "TOPS", "note": "the reference's Triton backend on this GPU, same operands; "
+                                         "context, not the reference arm"}
+
+
+def reference_gpu_triton_moe(device, name="large_rank_share"):
+    """Both libraries' moe_ffn on one expert-parallel rank's share of the large configuration:
+    the reference addresses weights with 32-bit offsets and cannot hold all 256 experts."""
+    module = reference_gpu_module()
+    if module is None:
+        return {}
+    import bench_moe
+    from grain_gemm_b200 import moe
+    case = bench_moe.make_case(name, device)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    try:
+        reference_ms = time_calls(lambda: module.moe_ffn(backend="triton", **case), start, stop)
+    except Exception as error:
+        return {"moe_unavailable": str(error).splitlines()[0][:200]}
+    ours_ms = time_calls(lambda: moe.moe_ffn(**case), start, stop)
+    tokens = case["hidden_states"].shape[0]
+    return {"moe_config": name, "moe_ms_per_step": reference_ms,
+            "moe_value": tokens / (reference_ms * 1e-3), "moe_unit": "tokens/s",
+            "moe_this_library_ms_per_step": ours_ms}
 
 
 def measured_peaks():
@@ -657,6 +718,13 @@ def main():
         except RuntimeError as error:
             library_probe = {"call": "torch._int_mm", "unavailable": str(error).splitlines()[0][:200]}
 
+    # Same-box context: what a B200 user of the reference gets today (its `auto` backend selects
+    # its Triton kernels on compute capability 10.0).  Only when the reference is installed
+    # beside the oracle; never part of a timed region of this library.
+    reference_gpu = None
+    if world == 1 and m > 16 and not args.skip_reference_gpu:
+        reference_gpu = reference_gpu_triton_gemm(a, b, scale_a, scale_b, g, start, stop)
+
     # End to end through the public API with host operands.
     e2e = None
     if not args.skip_e2e:
@@ -730,6 +798,10 @@ def main():
         line["sustained"] = sustained
     if library_probe is not None:
         line["int8_library_probe"] = library_probe
+    if reference_gpu is not None:
+        if world == 1 and args.moe_config != "none":
+            reference_gpu.update(reference_gpu_triton_moe(device))
+        line["reference_gpu_triton"] = reference_gpu
     if moe_result is not None:
         line["moe"] = moe_result
     if world == 1 and not args.skip_cpu_baseline:

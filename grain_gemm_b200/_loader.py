@@ -64,6 +64,7 @@ _SIGNATURES = {
     "gg_moe_combine": (_INT, [_VOID] * 4 + [_INT] * 4 + [_VOID]),
     "gg_device_status": (_INT, [ctypes.POINTER(_INT), _VOID]),
     "gg_selftest_wait_timeout": (_INT, [_LL, _VOID, _VOID]),
+    "gg_report_to_host": (_INT, [_VOID, _INT, _VOID, _VOID]),
 }
 
 EXPORTS = tuple(_SIGNATURES)

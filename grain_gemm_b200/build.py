@@ -24,7 +24,7 @@ CSRC = PACKAGE / "csrc"
 HEADER = PACKAGE.parent / "include" / "grain_gemm_b200.h"
 LIBRARY = PACKAGE / "libgrain_b200.so"
 MANIFEST = PACKAGE / "build.json"
-ABI_VERSION = 3
+ABI_VERSION = 4
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
          "-Xcompiler", "-fPIC", "-shared"]

@@ -19,7 +19,7 @@
 
 namespace gg {
 
-constexpr int kAbiVersion = 3;
+constexpr int kAbiVersion = 4;
 
 // ---------------------------------------------------------------- host helpers
 
@@ -104,15 +104,14 @@ static SplitKPlan splitk_plan(int m, int n, int k, int group_size) {
   SplitKPlan plan = {1, 0, 0};
   const int groups = (k + group_size - 1) / group_size;
   const int unit = group_size >= 128 ? 1 : 128 / group_size;   // ranges start on 128-byte slabs
-  const int tiles_n = (n + 255) / 256;
-  int splits = sm_count() / (tiles_n > 0 ? tiles_n : 1);
-  if (m > 32 || splits < 2 || groups < 2 * unit) return plan;
-  int per_split = (groups + splits - 1) / splits;
-  per_split = (per_split + unit - 1) / unit * unit;
-  splits = (groups + per_split - 1) / per_split;
+  if (m > 32 || n <= 0 || groups < 2 * unit) return plan;
+  // Finest ranges: the kernel hands every group's INT32 dots to the fold anyway, so a work item
+  // of one 128-byte-aligned range costs nothing extra, and tiles x ranges items spread evenly
+  // over all SMs whatever N is (a skinny GEMM is bound by how many SMs pull weights at once).
+  const int splits = (groups + unit - 1) / unit;
   if (splits < 2) return plan;
   plan.splits = splits;
-  plan.groups_per_split = per_split;
+  plan.groups_per_split = unit;
   plan.workspace_bytes = static_cast<size_t>(groups) * m * n * sizeof(int);
   return plan;
 }
@@ -1038,6 +1037,22 @@ int gg_moe_combine(const void* expert_out, const void* weights, const void* inve
         static_cast<const __half*>(expert_out), static_cast<const float*>(weights),
         static_cast<const int*>(inverse), static_cast<__half*>(out), top_k, hidden, vector_ok);
   }
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gg_report_to_host(const void* values, int count, void* host_words, void* stream_ptr) {
+  if (count <= 0) return 0;
+  if (count > 1024 || !values || !host_words) return static_cast<int>(cudaErrorInvalidValue);
+  // The destination must be page-locked host memory the device can address; its device-side
+  // address is asked for rather than assumed.
+  void* mapped = nullptr;
+  cudaError_t error = cudaHostGetDevicePointer(&mapped, host_words, 0);
+  if (error != cudaSuccess) {
+    (void)cudaGetLastError();
+    return static_cast<int>(error);
+  }
+  gg::report_to_host_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      static_cast<const int*>(values), count, static_cast<int*>(mapped));
   return static_cast<int>(cudaGetLastError());
 }
 

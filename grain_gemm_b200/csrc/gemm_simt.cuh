@@ -172,18 +172,18 @@ fold_partials_kernel(const int* __restrict__ partials, const float* __restrict__
   float total = 0.0f;
   const long long plane = static_cast<long long>(m) * n;
   const int* source = partials + static_cast<long long>(row) * n + col;
-  // Eight groups' loads are issued before their fused adds (which stay in group order).
+  // Sixteen groups' loads are issued before their fused adds (which stay in group order).
   int g = 0;
-  for (; g + 8 <= groups; g += 8) {
-    int dot[8];
-    float scale[8];
+  for (; g + 16 <= groups; g += 16) {
+    int dot[16];
+    float scale[16];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < 16; ++j) {
       dot[j] = source[(g + j) * plane];
       scale[j] = __fmul_rn(scale_a[row * sa_sm + (g + j) * sa_sg], scale_b[(g + j) * sb_sg + col * sb_sn]);
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) total = __fmaf_rn(__int2float_rn(dot[j]), scale[j], total);
+    for (int j = 0; j < 16; ++j) total = __fmaf_rn(__int2float_rn(dot[j]), scale[j], total);
   }
   for (; g < groups; ++g) {
     const float scale = __fmul_rn(scale_a[row * sa_sm + g * sa_sg], scale_b[g * sb_sg + col * sb_sn]);

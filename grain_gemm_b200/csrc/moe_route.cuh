@@ -179,6 +179,17 @@ __global__ void __launch_bounds__(kRouteChunk) route_place_kernel(const RoutePar
   route_place_chunk(p, s, present, key, bins);
 }
 
+// Hands a few integers (routing statistics, error flags) to the host by storing them into
+// page-locked host memory the device can address.  Unlike a device-to-host copy this does not
+// queue behind other transfers on the copy engine, so a caller that streams large results to
+// the host at the same time still learns the values as soon as the producing kernel is done,
+// and the stream does not wait for the copy engine either.
+__global__ void __launch_bounds__(32)
+report_to_host_kernel(const int* __restrict__ values, int count, int* host_words) {
+  for (int i = threadIdx.x; i < count; i += 32) host_words[i] = values[i];
+  __threadfence_system();
+}
+
 // Row-tile list for the grouped kernels: every expert's sorted rows are cut into tiles of
 // `tile_rows`; tile_expert/tile_row have room for ceil(S / tile_rows) + E entries, unused
 // entries get expert -1.  One CTA.

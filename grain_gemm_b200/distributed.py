@@ -255,9 +255,9 @@ class PeerExchange:
         self.row_mask = make((rows,), torch.uint8)
         self.row_destination = make((rows * top_k,), torch.int64)
         self.flags = make((2,), torch.int32)           # [0] = a kernel refused an index
+        self.report = make((world + 2,), torch.int32)  # invalid-id counts per rank, then flags
         self.tables = None
         self.workspace = moe.MoEWorkspace()
-        self._host = torch.empty((world + 3,), dtype=torch.int32).pin_memory()
 
     # -- construction ----------------------------------------------------------------------
 
@@ -416,12 +416,11 @@ def _peer_step(exchange, hidden_states, w_gate_up, w_down, topk_weights, topk_id
     mark()
     # Invalid ids and refused indices are read back while the combine runs (not under capture).
     capturing = torch.cuda.is_current_stream_capturing()
-    host = exchange._host
     if not capturing:
-        host[:world].copy_(exchange.counts_all[:, world], non_blocking=True)
-        host[world:world + 2].copy_(exchange.flags, non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
+        from . import moe
+        exchange.report[:world].copy_(exchange.counts_all[:, world])
+        exchange.report[world:].copy_(exchange.flags)
+        host, event = moe._statistics_readback(exchange.report, world + 2, slot="expert_parallel")
     out = exchange.combine(topk_weights)
     mark()
     if not capturing:

@@ -308,22 +308,31 @@ def combine(expert_output, topk_weights, routes, *, output_dtype=torch.bfloat16)
 _HOST = threading.local()
 
 
-def _statistics_readback(statistics):
-    """Start an asynchronous copy of the routing statistics to pinned host memory.
+def _statistics_readback(statistics, count=3, slot="statistics"):
+    """Start handing ``count`` integers of ``statistics`` to pinned host memory.
 
-    Returns ``(host_tensor, event)``; the event completes as soon as routing has run, so a
-    caller that first launches the remaining stages and only then waits on it never leaves the
-    GPU idle.  One pinned buffer per thread and device is reused: a call's readback is consumed
-    before the same thread can start another call.
+    Returns ``(host_tensor, event)``; the event completes as soon as the kernels before it have
+    run, so a caller that first launches the remaining stages and only then waits on it never
+    leaves the GPU idle.  The integers are stored by a kernel (``gg_report_to_host``), not by
+    a copy: a device-to-host copy would queue behind whatever large transfer the application
+    has on the copy engine (the previous call's result on its way to the host, say), and the
+    stream, and with it the remaining stages, would wait for it.  One pinned buffer per thread,
+    device and ``slot`` is reused: a call's readback is consumed before the same thread can
+    start another call.
     """
+    from . import _loader
     buffers = getattr(_HOST, "buffers", None)
     if buffers is None:
         buffers = _HOST.buffers = {}
-    key = statistics.device.index
+    key = (statistics.device.index, slot, count)
     if key not in buffers:
-        buffers[key] = torch.empty((3,), dtype=torch.int32, pin_memory=True)
+        buffers[key] = torch.empty((count,), dtype=torch.int32, pin_memory=True)
     host = buffers[key]
-    host.copy_(statistics, non_blocking=True)
+    status = _loader.library().gg_report_to_host(
+        _loader.pointer(statistics), count, host.data_ptr(), _loader.stream_pointer(statistics.device))
+    if status != 0:
+        # Host memory the device cannot address: fall back to the copy engine.
+        host.copy_(statistics.reshape(-1)[:count], non_blocking=True)
     event = torch.cuda.Event()
     event.record()
     return host, event

@@ -314,6 +314,17 @@ int gg_peer_release(void* pointer);
 int gg_device_status(int* status, void* stream);
 
 /*
+ * Stores count (1 .. 1024) 32-bit words from device memory into page-locked host memory from
+ * a kernel on `stream` (no counterpart in the reference, which reads its routing statistics back
+ * with a blocking copy, src/grain_gemm/moe.py:258-260).  host_words
+ * must come from cudaHostAlloc / cudaHostRegister (torch pinned memory does); the call asks
+ * the driver for its device-side address and returns the driver's error if there is none.  A
+ * copy engine busy with other transfers does not delay it.  The caller orders its read with an
+ * event recorded after the call.
+ */
+int gg_report_to_host(const void* values, int count, void* host_words, void* stream);
+
+/*
  * Self-test of that mechanism (no counterpart in the reference, whose device waits are
  * unbounded): launches one warp that waits, with the kernels' own bounded wait, on a barrier
  * nothing ever completes.  The wait gives up after limit_ns nanoseconds (1 .. 100 000 000), the

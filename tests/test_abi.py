@@ -65,6 +65,10 @@ def test_null_pointers_are_rejected_before_any_launch(library):
     assert library.gg_selftest_wait_timeout(0, fake, null) == 1
     assert library.gg_moe_silu_table(null, 1, null) == 1
     assert library.gg_moe_silu_table(fake, 0, null) == 1
+    assert library.gg_report_to_host(null, 3, fake, null) == 1
+    assert library.gg_report_to_host(fake, 3, null, null) == 1
+    assert library.gg_report_to_host(fake, 1025, fake, null) == 1
+    assert library.gg_report_to_host(null, 0, null, null) == 0      # nothing to report
 
 
 def test_stale_library_is_refused(library, monkeypatch):

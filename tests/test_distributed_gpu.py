@@ -63,7 +63,52 @@ def test_peer_exchange_with_all_ranks_on_one_gpu_matches_single_gpu_bits(world, 
     assert _loader.device_status() == 0
 
 
-def worker(rank, world, port, results):
+def captured_step(distributed, exchange, static):
+    """Capture one expert-parallel step over the tensors of ``static`` into a CUDA graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):                # warm-up: buffers of the workspace, function attributes
+            distributed.moe_ffn_expert_parallel(**static, exchange=exchange)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = distributed.moe_ffn_expert_parallel(**static, exchange=exchange)
+    return graph, out
+
+
+def test_peer_exchange_step_replays_from_a_cuda_graph_with_new_routing():
+    """The peer-memory step has no host read-back on its path, so a whole step (plan, dispatch,
+    routing, Gate/Up, Down into home_out, combine) is one CUDA graph; replays follow the token
+    rows, ids and weights written into the captured tensors."""
+    import bench_moe
+    from grain_gemm_b200 import _loader, distributed, moe
+    device = torch.device("cuda")
+    bench_moe.CONFIGS["ep_test"] = dict(EP_TEST)
+    case = bench_moe.make_case("ep_test", device)
+    exchange = distributed.PeerExchange.local_ranks(
+        1, capacity=768, hidden=1024, top_k=4, local_experts=16, device=device)[0]
+    try:
+        static = dict(case, num_experts=16)
+        graph, out = captured_step(distributed, exchange, static)
+        generator = torch.Generator(device="cuda").manual_seed(11)
+        for repeat in range(3):
+            ids = torch.randint(0, 16, (768, 4), device=device, generator=generator,
+                                dtype=case["topk_ids"].dtype)
+            x = torch.randint(-127, 128, (768, 1024), device=device, generator=generator,
+                              dtype=torch.int8)
+            static["topk_ids"].copy_(ids)
+            static["hidden_states"].copy_(x)
+            graph.replay()
+            expected = moe.moe_ffn(**case)          # `case` shares the captured tensors
+            assert torch.equal(out, expected), repeat
+    finally:
+        exchange.close()
+    assert _loader.device_status() == 0
+
+
+def worker(rank, world, port, results, from_graph=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     try:
         torch.cuda.set_device(rank)
@@ -86,9 +131,19 @@ def worker(rank, world, port, results):
         via_peers = [distributed.moe_ffn_expert_parallel(**local, num_experts=16, exchange=exchange)
                      for _ in range(3)]
         torch.cuda.synchronize()
+        replays = []
+        if from_graph:
+            # The same step from a CUDA graph (the two small collectives are captured with it).
+            graph, captured_out = captured_step(distributed, exchange, dict(local, num_experts=16))
+            for _ in range(2):
+                captured_out.zero_()
+                graph.replay()
+                torch.cuda.synchronize()
+                replays.append(bool(torch.equal(captured_out, single[rows])))
+            del graph
         results[rank] = ("ok", bool(torch.equal(via_nccl, single[rows])),
-                         all(bool(torch.equal(out, single[rows])) for out in via_peers),
-                         _loader.device_status())
+                         all(bool(torch.equal(out, single[rows])) for out in via_peers)
+                         and all(replays), _loader.device_status())
         dist.barrier()
         exchange.close()
         dist.barrier()
@@ -108,4 +163,18 @@ def test_expert_parallel_matches_single_gpu_bits(world):
     results = mp.Manager().dict()
     mp.spawn(worker, args=(world, port, results), nprocs=world, join=True)
     for rank in range(world):
+        assert results[rank] == ("ok", True, True, 0), results[rank]
+
+
+def test_expert_parallel_step_replays_from_a_cuda_graph_on_two_gpus():
+    """The peer-memory step with its count all-gather and its 2-int all-reduce inside one CUDA
+    graph per rank; replays are bit-identical to one GPU."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with socket.socket() as probe:
+        probe.bind(("127.0.0.1", 0))
+        port = probe.getsockname()[1]
+    results = mp.Manager().dict()
+    mp.spawn(worker, args=(2, port, results, True), nprocs=2, join=True)
+    for rank in range(2):
         assert results[rank] == ("ok", True, True, 0), results[rank]

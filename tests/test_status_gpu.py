@@ -50,3 +50,27 @@ def test_selftest_rejects_unbounded_limits():
     for limit in (0, -5, 100_000_001):
         assert lib.gg_selftest_wait_timeout(limit, _loader.pointer(result), None) == 1
     assert lib.gg_selftest_wait_timeout(1000, ctypes.c_void_p(0), None) == 1
+
+
+def test_report_to_host_stores_words_in_pinned_memory():
+    """The routing statistics reach the host through a kernel store into page-locked memory
+    (no copy engine involved); memory the device cannot address is refused with the driver's
+    error before any launch."""
+    from grain_gemm_b200 import _loader
+
+    lib = _loader.library()
+    values = torch.arange(100, 137, dtype=torch.int32, device="cuda")
+    host = torch.zeros((37,), dtype=torch.int32).pin_memory()
+    status = lib.gg_report_to_host(_loader.pointer(values), 37, host.data_ptr(),
+                                   _loader.stream_pointer(values.device))
+    assert status == 0
+    torch.cuda.synchronize()
+    assert host.tolist() == list(range(100, 137))
+    pageable = torch.zeros((64,), dtype=torch.int32)
+    refused = lib.gg_report_to_host(_loader.pointer(values), 3, pageable.data_ptr(),
+                                    _loader.stream_pointer(values.device))
+    torch.cuda.synchronize()
+    # Either the driver has no device address for pageable memory (the usual answer: nothing is
+    # launched, nothing is written) or the system maps all host memory and the words arrive.
+    assert pageable[:3].tolist() == ([0, 0, 0] if refused else [100, 101, 102])
+    assert _loader.device_status() == 0
