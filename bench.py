@@ -419,8 +419,8 @@ def run_moe(args, rank, world, device, barrier):
     # Phase times of the expert-parallel step (rank 0's events; no extra synchronisation).
     phases = None
     if exchange is not None:
-        names = ["plan_and_dispatch", "count_all_gather", "local_experts", "results_home_all_reduce",
-                 "combine"]
+        names = ["plan_and_dispatch", "count_all_gather", "mask_and_route", "gather_and_gate_up",
+                 "down_into_home_ranks", "results_home_all_reduce", "combine"]
         totals = [0.0] * len(names)
         for _ in range(steps):
             marks = []
@@ -545,23 +545,29 @@ def run_moe(args, rank, world, device, barrier):
     return report
 
 
-SWEEP_M = [1, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192]
+SWEEP_M = [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192]
 SWEEP_NK = [(8192, 8192), (4096, 4096), (4096, 7168), (7168, 2048), (28672, 4096), (4096, 14336)]
-SWEEP_VARIANTS = ["tc_n256", "tc_n128", "tc_n64", "tc_pair_n256", "tc_pair_n128", "tc_splitk"]
+SWEEP_VARIANTS = ["tc_n256", "tc_n128", "tc_n64", "tc_pair_n256", "tc_pair_n128", "tc_splitk", "gemv"]
 
 
 def run_sweep(args, device):
-    """Times every tensor-core variant on M x (N, K) x G and writes, per (G, N, K), the fastest
-    variant for each M bucket (the table ``get_kernel_config`` / ``int8_gemm`` consult)."""
+    """Times every variant on M x (N, K) x G and writes, per (G, N, K), the fastest variant for
+    each M bucket (the table ``get_kernel_config`` / ``int8_gemm`` consult).  Launches are
+    replayed from a CUDA graph, so that microsecond kernels are not timed by the host's launch
+    rate, and walk through several copies of the weights (more than the L2 holds), as the
+    layers of a model would."""
     from grain_gemm_b200 import _loader, gemm
 
     lib = _loader.library()
     shapes, timings = {}, {}
+    side = torch.cuda.Stream(device)
     for g in (256, 128, 64, 32):
         for n, k in SWEEP_NK:
             rows = []
+            copies = max(1, min(8, int(140e6 // (n * k)) + 1))
+            weights = [make_gemm_inputs(1, n, k, g, 7 + c, device)[1] for c in range(copies)]
             for m in SWEEP_M:
-                a, w, scale_a, scale_b = make_gemm_inputs(m, n, k, g, 7, device)
+                a, _, scale_a, scale_b = make_gemm_inputs(m, n, k, g, 7, device)
                 out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
                 best = None
                 for variant in SWEEP_VARIANTS:
@@ -569,20 +575,30 @@ def run_sweep(args, device):
                         continue
                     if variant.startswith("tc_pair") and m <= 128:
                         continue
+                    if variant == "gemv" and m > 8:
+                        continue
                     try:
-                        for _ in range(3):
+                        for w in weights[:2]:
                             gemm.launch(a, w.t(), scale_a, scale_b, out, g, variant)
                     except RuntimeError:
                         continue
                     torch.cuda.synchronize()
+                    rounds = max(1, (12 if m * n * k < 2 ** 36 else 3) // copies)
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.stream(side):
+                        with torch.cuda.graph(graph, stream=side):
+                            for _ in range(rounds):
+                                for w in weights:
+                                    gemm.launch(a, w.t(), scale_a, scale_b, out, g, variant)
+                    graph.replay()
+                    torch.cuda.synchronize()
                     start, stop = (torch.cuda.Event(enable_timing=True) for _ in range(2))
-                    iterations = 20 if m * n * k < 2 ** 36 else 5
                     start.record()
-                    for _ in range(iterations):
-                        gemm.launch(a, w.t(), scale_a, scale_b, out, g, variant)
+                    graph.replay()
                     stop.record()
                     torch.cuda.synchronize()
-                    microseconds = start.elapsed_time(stop) / iterations * 1e3
+                    microseconds = start.elapsed_time(stop) / (rounds * copies) * 1e3
+                    del graph
                     timings[f"{g}:{n}:{k}:{m}:{variant}"] = round(microseconds, 2)
                     if best is None or microseconds < best[0]:
                         best = (microseconds, variant)
@@ -591,7 +607,8 @@ def run_sweep(args, device):
                         rows[-1][0] = m
                     else:
                         rows.append([m, best[1]])
-                del a, w, scale_a, scale_b, out
+                del a, scale_a, scale_b, out
+            del weights
             if rows:
                 rows[-1][0] = 2 ** 31 - 1
                 shapes[f"{g}:{n}:{k}"] = rows

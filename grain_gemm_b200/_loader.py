@@ -24,7 +24,7 @@ _SIZE = ctypes.c_size_t
 OUT_DTYPE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 VARIANTS = {
     "auto": 0, "simt": 1, "tc_n256": 2, "tc_n128": 3, "tc_n64": 4,
-    "tc_pair_n256": 5, "tc_pair_n128": 6, "tc_splitk": 7,
+    "tc_pair_n256": 5, "tc_pair_n128": 6, "tc_splitk": 7, "gemv": 8,
 }
 VARIANT_NAMES = {value: key for key, value in VARIANTS.items()}
 

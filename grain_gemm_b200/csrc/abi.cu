@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "../../include/grain_gemm_b200.h"
+#include "gemm_gemv.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "moe_ep.cuh"
@@ -87,6 +88,9 @@ struct GemmArgs {
 
 static bool valid_group(int g) { return g == 32 || g == 64 || g == 128 || g == 256; }
 
+// Largest M the automatic choice gives to the weight-streaming kernel.
+constexpr int GEMV_AUTO_ROWS = 2;
+
 static bool tensor_core_layout(const GemmArgs& g) {
   return g.a_sk == 1 && g.b_sk == 1 && g.a_sm % 16 == 0 && g.b_sn % 16 == 0 && g.a_sm >= g.k &&
          g.b_sn >= g.k && aligned16(g.a) && aligned16(g.b);
@@ -116,8 +120,100 @@ static SplitKPlan splitk_plan(int m, int n, int k, int group_size) {
   return plan;
 }
 
+// The weight-streaming kernel takes the tensor-core kernels' operand layout and whole 16-byte
+// chunks of K.
+static int gemv_rows(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : 8; }
+
+static size_t gemv_smem_bytes(const GemmArgs& g, int columns) {
+  const size_t rows = static_cast<size_t>(gemv_rows(g.m));
+  const size_t groups = static_cast<size_t>((g.k + g.group_size - 1) / g.group_size);
+  return groups * (rows * columns + columns + rows) * sizeof(int);
+}
+
+// The kernel instantiation for (rows, lanes per K group): every combination exists.
+typedef void (*GemvKernel)(const GemvParams);
+
+template <int kRows>
+static GemvKernel gemv_kernel_for_group(int group_size) {
+  switch (group_size) {
+    case 32: return gemm_gemv_kernel<kRows, 2>;
+    case 64: return gemm_gemv_kernel<kRows, 4>;
+    case 128: return gemm_gemv_kernel<kRows, 8>;
+    default: return gemm_gemv_kernel<kRows, 16>;
+  }
+}
+
+static GemvKernel gemv_kernel(int rows, int group_size) {
+  switch (rows) {
+    case 1: return gemv_kernel_for_group<1>(group_size);
+    case 2: return gemv_kernel_for_group<2>(group_size);
+    case 4: return gemv_kernel_for_group<4>(group_size);
+    default: return gemv_kernel_for_group<8>(group_size);
+  }
+}
+
+// CTAs of the kernel that one SM holds (registers decide; asked once per row count).
+static int gemv_ctas_per_sm(int rows) {
+  static int cached[4] = {0, 0, 0, 0};
+  const int index = rows == 1 ? 0 : rows == 2 ? 1 : rows == 4 ? 2 : 3;
+  if (cached[index] == 0) {
+    int blocks = 0;
+    const cudaError_t error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+        &blocks, gemv_kernel(rows, 256), kGemvThreads, 4096);
+    if (error != cudaSuccess) (void)cudaGetLastError();
+    cached[index] = error == cudaSuccess && blocks > 0 ? blocks : 2;
+  }
+  return cached[index];
+}
+
+// Columns per warp (0 = not eligible): the fewest for which all CTAs of the launch are resident
+// at once, as long as a CTA's per-group dots and scales fit 96 KB of shared memory.
+static int gemv_columns_per_warp(const GemmArgs& g) {
+  if (!tensor_core_layout(g) || g.m < 1 || g.m > kGemvMaxRows || g.k % 16 != 0) return 0;
+  const long long resident = static_cast<long long>(sm_count()) * gemv_ctas_per_sm(gemv_rows(g.m));
+  int per_warp = 1;
+  while (per_warp < kGemvMaxColumnsPerWarp &&
+         (g.n + kGemvWarps * per_warp - 1) / (kGemvWarps * per_warp) > resident) {
+    ++per_warp;
+  }
+  while (per_warp > 1 && gemv_smem_bytes(g, kGemvWarps * per_warp) > 96 * 1024) --per_warp;
+  return gemv_smem_bytes(g, kGemvWarps * per_warp) <= 96 * 1024 ? per_warp : 0;
+}
+
+static bool gemv_eligible(const GemmArgs& g) { return gemv_columns_per_warp(g) != 0; }
+
+static int launch_gemv(const GemmArgs& g, cudaStream_t stream) {
+  const int per_warp = gemv_columns_per_warp(g);
+  if (per_warp == 0) return static_cast<int>(cudaErrorInvalidValue);
+  GemvParams p = {};
+  p.a = static_cast<const int8_t*>(g.a);
+  p.b = static_cast<const int8_t*>(g.b);
+  p.scale_a = static_cast<const float*>(g.scale_a);
+  p.scale_b = static_cast<const float*>(g.scale_b);
+  p.c = g.c;
+  p.m = g.m; p.n = g.n; p.k = g.k;
+  p.group_size = g.group_size;
+  p.out_dtype = g.out_dtype;
+  p.a_sm = g.a_sm; p.b_sn = g.b_sn;
+  p.sa_sm = g.sa_sm; p.sa_sg = g.sa_sg; p.sb_sg = g.sb_sg; p.sb_sn = g.sb_sn;
+  p.ldc = g.ldc;
+  p.columns_per_warp = per_warp;
+  const int columns = kGemvWarps * per_warp;
+  const size_t smem = gemv_smem_bytes(g, columns);
+  const unsigned grid = static_cast<unsigned>((g.n + columns - 1) / columns);
+  const GemvKernel kernel = gemv_kernel(gemv_rows(g.m), g.group_size);
+  if (smem > 48 * 1024) {
+    const cudaError_t error = cudaFuncSetAttribute(
+        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (error != cudaSuccess) return static_cast<int>(error);
+  }
+  kernel<<<grid, kGemvThreads, smem, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 static int select_variant(const GemmArgs& g) {
   if (!tensor_core_layout(g)) return GG_VARIANT_SIMT;
+  if (g.m <= GEMV_AUTO_ROWS && gemv_eligible(g)) return GG_VARIANT_GEMV;
   const int sms = sm_count();
   const long long tiles_256 = static_cast<long long>((g.m + 127) / 128) * ((g.n + 255) / 256);
   if (splitk_plan(g.m, g.n, g.k, g.group_size).splits >= 2) return GG_VARIANT_TC_SPLITK;
@@ -338,6 +434,7 @@ static int run_gemm(const GemmArgs& g, int variant, cudaStream_t stream, void* w
     return launch_simt_dtype<false>(simt_params(g), (g.m + kSimtTile - 1) / kSimtTile, g.out_dtype,
                                     stream);
   }
+  if (variant == GG_VARIANT_GEMV) return launch_gemv(g, stream);
   if (variant < GG_VARIANT_TC_N256 || variant > GG_VARIANT_TC_PAIR_N128 || !tensor_core_layout(g)) {
     return static_cast<int>(cudaErrorInvalidValue);
   }

@@ -722,6 +722,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               c_row = reinterpret_cast<OutT*>(destination);
             }
           }
+          if constexpr (kGrouped && sizeof(OutT) == 2 && kBlocks % 2 == 0) {
+            // Rows that leave for another GPU's memory: lanes 16 apart (rows 4 apart) swap one
+            // of two neighbouring blocks, so that a store instruction covers four rows with 128
+            // contiguous bytes each instead of eight rows with 64; a link carries full cache
+            // lines better than halves.  All conditions are the same in every lane.
+            if (p.row_destination != nullptr && aligned && n0 + col_base + kNC <= p.n) {
+              const bool low = fragment_row < 4;
+              const int partner_row = out_row + (low ? 4 : -4);
+              const unsigned long long partner_destination =
+                  partner_row < row_limit ? p.row_destination[partner_row] : 0ull;
+#pragma unroll
+              for (int block = 0; block < kBlocks; block += 2) {
+                uint32_t w[2][4];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) w[half][i] = pack_pair<OutT>(acc[r][(block + half) * 4 + i]);
+                  quad_transpose(w[half], quad);
+                  if constexpr (kLayout == kFragmentQuads) {
+                    const uint32_t v0 = w[half][0], v1 = w[half][1], v2 = w[half][2], v3 = w[half][3];
+                    w[half][0] = __byte_perm(v0, v1, 0x5410);
+                    w[half][1] = __byte_perm(v2, v3, 0x5410);
+                    w[half][2] = __byte_perm(v0, v1, 0x7632);
+                    w[half][3] = __byte_perm(v2, v3, 0x7632);
+                  }
+                }
+                // Low lanes keep block `block` and give away the next one, high lanes the reverse.
+                uint32_t received[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  received[i] = __shfl_xor_sync(0xffffffffu, low ? w[1][i] : w[0][i], 16);
+                }
+                const int col = n0 + col_base + (block + (low ? 0 : 1)) * 32 + 8 * quad;
+                // First the rows of the low lanes, then the rows of the high lanes.
+                const unsigned long long first = low ? reinterpret_cast<unsigned long long>(c_row)
+                                                     : partner_destination;
+                const unsigned long long second = low ? partner_destination
+                                                      : reinterpret_cast<unsigned long long>(c_row);
+                const bool first_stored = low ? row_stored : partner_destination != 0ull;
+                const bool second_stored = low ? partner_destination != 0ull : row_stored;
+                const uint4 own = low ? make_uint4(w[0][0], w[0][1], w[0][2], w[0][3])
+                                      : make_uint4(w[1][0], w[1][1], w[1][2], w[1][3]);
+                const uint4 other = make_uint4(received[0], received[1], received[2], received[3]);
+                if (first_stored) {
+                  *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(first) + col) = low ? own : other;
+                }
+                if (second_stored) {
+                  *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(second) + col) = low ? other : own;
+                }
+              }
+              continue;
+            }
+          }
 #pragma unroll
           for (int block = 0; block < kBlocks; ++block) {
             const int col = n0 + col_base + block * 32 + 8 * quad;

@@ -351,9 +351,11 @@ class PeerExchange:
             _loader.pointer(self.flags), stream), "gg_ep_dispatch")
         return self.counts
 
-    def experts(self, counts_all, w_gate_up, w_down, scale_gate_up, scale_down, gate_up_layout):
+    def experts(self, counts_all, w_gate_up, w_down, scale_gate_up, scale_down, gate_up_layout,
+                mark=None):
         """Stages 1-3 on the rows that arrived; Down stores each result row into the home
-        rank's ``home_out``.  ``counts_all`` is the all-gathered ``[world, world + 1]`` matrix."""
+        rank's ``home_out``.  ``counts_all`` is the all-gathered ``[world, world + 1]`` matrix.
+        ``mark``, a callable, is invoked after routing and after Gate/Up (timing events)."""
         from . import _loader, moe
         stream = _loader.stream_pointer(self.device)
         _loader.check(self._lib.gg_ep_row_mask(
@@ -361,9 +363,13 @@ class PeerExchange:
             _loader.pointer(self.row_mask), stream), "gg_ep_row_mask")
         routes = moe.prepare_routes(self.recv_ids, self.local_experts, self.row_mask,
                                     tile_rows=moe.TENSOR_CORE_TILE_ROWS, workspace=self.workspace)
+        if mark is not None:
+            mark()
         qh, sh = moe.gate_up_swiglu_quantize(
             self.recv_x, self.recv_scale, w_gate_up.transpose(-2, -1), scale_gate_up, routes,
             output_dtype=self.output_dtype, gate_up_layout=gate_up_layout, workspace=self.workspace)
+        if mark is not None:
+            mark()
         _loader.check(self._lib.gg_ep_row_destination(
             _loader.pointer(routes.order), _loader.pointer(routes.offsets), self.local_experts,
             self.top_k, self.capacity, self.world, self.hidden, _loader.OUT_DTYPE[self.output_dtype],
@@ -385,8 +391,8 @@ class PeerExchange:
 def _peer_step(exchange, hidden_states, w_gate_up, w_down, topk_weights, topk_ids, scale_x,
                scale_gate_up, scale_down, token_mask, gate_up_layout, marks=None):
     """One expert-parallel FFN through ``exchange`` (see ``PeerExchange``).  ``marks``, a list,
-    receives timing events at the phase boundaries (start, dispatched, counts gathered, experts
-    done, results home, combined)."""
+    receives timing events at the phase boundaries (start, dispatched, counts gathered, routed,
+    Gate/Up done, Down done, results home, combined)."""
     world, group = exchange.world, exchange.group
 
     def mark():
@@ -408,7 +414,7 @@ def _peer_step(exchange, hidden_states, w_gate_up, w_down, topk_weights, topk_id
         exchange.counts_all.copy_(counts.reshape(1, -1))
     mark()
     exchange.experts(exchange.counts_all, w_gate_up, w_down, scale_gate_up, scale_down,
-                     gate_up_layout)
+                     gate_up_layout, mark=mark if marks is not None else None)
     mark()
     # "All results are home" (and any refused index on any rank) before the combine.
     if world > 1:

@@ -152,13 +152,14 @@ def get_kernel_config(a, b, *, group_size=256, output_dtype=torch.bfloat16,
     name = _loader.VARIANT_NAMES[variant]
     policy = "sm100_native"
     tabled = _table_variant(m, n, k, group_size)
-    if tabled is not None and name.startswith("tc"):
+    if tabled is not None and (name.startswith("tc") or name == "gemv"):
         name, policy = tabled, "sm100_table"
     pair = name.startswith("tc_pair")
     block_n = (256 if name == "tc_splitk" else int(name.split("_n", 1)[1].split("_")[0])
-               if name.startswith("tc") else 32)
+               if name.startswith("tc") else 8 if name == "gemv" else 32)
+    block_m = ((256 if pair else 128) if name.startswith("tc") else 8 if name == "gemv" else 32)
     return dict(policy=policy, compute_capability=list(capability), backend="cuda",
-                variant=name, block_m=(256 if pair else 128) if name.startswith("tc") else 32,
+                variant=name, block_m=block_m,
                 block_n=block_n, cta_group=2 if pair else 1,
                 tensor_cores=name.startswith("tc"), repacked_a=repack_a, repacked_b=repack_b)
 

@@ -34,6 +34,7 @@ extern "C" {
 #define GG_VARIANT_TC_PAIR_N256 5 /* tcgen05 cta_group::2, CTA pair per 256 x 256 tile */
 #define GG_VARIANT_TC_PAIR_N128 6 /* tcgen05 cta_group::2, CTA pair per 256 x 128 tile */
 #define GG_VARIANT_TC_SPLITK 7   /* tcgen05, M <= 32: K split over CTAs, INT32 dots folded in order */
+#define GG_VARIANT_GEMV 8        /* CUDA cores (dp4a), M <= 8, K % 16 == 0: weights streamed once, no workspace */
 
 /* ABI version of this header; the Python loader refuses a library that reports another. */
 int gg_abi_version(void);

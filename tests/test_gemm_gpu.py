@@ -210,8 +210,30 @@ def test_split_k_for_skinny_m_is_bit_exact(gg, m, n, k, g):
         assert torch.equal(run(gg, tensors, g, dtype, "tc_splitk"), expected)
     a, b, _, _ = (t.cuda() for t in tensors)
     config = gg.get_kernel_config(a, b, group_size=g)
-    # The library's own rule splits K for these shapes; a measured table entry may overrule it.
-    assert config["variant"] == "tc_splitk" or config["policy"] == "sm100_table"
+    # The library's own rule splits K for these shapes (one or two rows stream the weights on
+    # CUDA cores instead); a measured table entry may overrule it.
+    assert config["variant"] == ("gemv" if m <= 2 else "tc_splitk") or config["policy"] == "sm100_table"
+
+
+@pytest.mark.parametrize("g", [32, 64, 128, 256])
+@pytest.mark.parametrize("m,n,k", [(1, 2048, 4096), (2, 37, 4000), (3, 1000, 2080), (4, 8192, 8192),
+                                   (5, 520, 16), (8, 4096, 7168), (1, 7, 272)])
+def test_weight_streaming_kernel_for_a_handful_of_rows_is_bit_exact(gg, m, n, k, g):
+    """The CUDA-core kernel for M <= 8 (dp4a dots per group, ordered fold): ragged N, K tails
+    that end inside a group and inside a lane's range, every group size and output type."""
+    tensors = linear_case(m, n, k, g, seed=3 * m + g, scale="lognormal")
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        expected = oracle.int8_gemm(*tensors, g, dtype)
+        assert torch.equal(run(gg, tensors, g, dtype, "gemv"), expected)
+    a, b, _, _ = (t.cuda() for t in tensors)
+    if m <= 2:
+        config = gg.get_kernel_config(a, b, group_size=g)
+        assert config["variant"] == "gemv" or config["policy"] == "sm100_table"
+    # More than eight rows, or a K that is not a whole number of 16-byte chunks, is refused.
+    with pytest.raises(RuntimeError):
+        run(gg, linear_case(9, 64, 256, g, seed=1, scale="lognormal"), g, torch.float32, "gemv")
+    with pytest.raises(RuntimeError):
+        run(gg, linear_case(2, 64, 264, g, seed=1, scale="lognormal"), g, torch.float32, "gemv")
 
 
 @pytest.mark.parametrize("m", [1, 16, 128])
