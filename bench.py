@@ -16,6 +16,10 @@ token rows and results travel through peer memory from inside the dispatch and D
 The ``moe`` block carries its own roofline, CPU baseline, end-to-end figure, per-phase times
 and, at N > 1, a bit-identity check of the expert-parallel result against one GPU.
 
+``reference_gpu_triton`` (N = 1, when ``oracle/make_ref.py`` has installed the reference beside
+the oracle) times the reference's own Triton path on this GPU on the same operands: context for
+what a B200 user of the reference gets today, outside every timed region of this library.
+
 ``--impl reference`` times the reference's CPU path for the same metric: the CPU oracle
 (``oracle/``, a restatement of the reference's arithmetic; the reference ships no compiled
 CPU implementation) on the whole workload, all host threads.
@@ -479,7 +483,9 @@ def run_moe(args, rank, world, device, barrier):
     e2e_elapsed = torch.tensor([start.elapsed_time(stop) / steps], device=device)
     if world > 1:
         dist.all_reduce(e2e_elapsed, op=dist.ReduceOp.MAX)
-    stages = bench_moe.time_stages(case, steps=3, warmup=1) if world == 1 else None
+    # Same number of back-to-back calls as the timed loop, so that the stage sum and the call
+    # time are taken at comparable clocks (the part is power-managed).
+    stages = bench_moe.time_stages(case, steps=steps, warmup=3) if world == 1 else None
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         cpu = cpu_moe_sample(name, case, device)
@@ -524,9 +530,10 @@ def run_moe(args, rank, world, device, barrier):
                 "h2d_bytes_per_step": world * sum(t.numel() * t.element_size() for t in host.values()),
                 "d2h_bytes_per_step": world * host_out.numel() * host_out.element_size(),
                 "ms_per_step": e2e_ms},
-        # route (1 or 3), tiles, row copy, SiLU table, Gate/Up, Down, combine; the
-        # expert-parallel step adds plan, dispatch, row mask and row destinations.
-        "gpu_launches_per_step": 9 if world == 1 else 13,
+        # route (3), tiles, statistics report, row copy, SiLU table, Gate/Up, Down, combine;
+        # the expert-parallel step adds plan, dispatch, row mask and row destinations (its two
+        # small copies into the report buffer and its two NCCL collectives are not counted).
+        "gpu_launches_per_step": 10 if world == 1 else 14,
     }
     if stages is not None:
         report["stage_ms"] = stages

@@ -79,7 +79,7 @@ __device__ __forceinline__ void gemv_step(const GemvParams& p, const uint4& w, i
 }
 
 template <int kRows, int kLanesPerGroup>
-__global__ void __launch_bounds__(kGemvThreads) gemm_gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGemvThreads, kRows <= 2 ? 4 : 2) gemm_gemv_kernel(const GemvParams p) {
   extern __shared__ int gemv_dots[];             // [C][kRows][Q], C = columns of this CTA
   const int groups = (p.k + p.group_size - 1) / p.group_size;
   const int columns = kGemvWarps * p.columns_per_warp;
@@ -121,29 +121,25 @@ __global__ void __launch_bounds__(kGemvThreads) gemm_gemv_kernel(const GemvParam
   for (int block = 0; block < blocks; ++block) {
     int* dots = gemv_dots + (warp * p.columns_per_warp + column) * kRows * groups;
     const int base = block_in_column * 256 + lane;
-    uint4 current[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) current[j] = w[j];
-    // The next block's loads (of this column or the next) go out before this block's arithmetic.
+    // Where the next block's weights are (the same column or the next one).
     if (++block_in_column == blocks_per_column) {
       block_in_column = 0;
       ++column;
     }
-    if (block + 1 < blocks) {
-      const int8_t* next = p.b + static_cast<long long>(warp_first + column) * p.b_sn;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int chunk = block_in_column * 256 + j * 32 + lane;
-        w[j] = chunk < chunks ? ldg_stream_16(next + (static_cast<long long>(chunk) << 4))
-                              : make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
+    const bool more = block + 1 < blocks;
+    const int8_t* next = p.b + static_cast<long long>(warp_first + (more ? column : 0)) * p.b_sn;
+    const int next_base = block_in_column * 256 + lane;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       // Whole-warp condition: the shuffles inside always see 32 lanes.
       if (base - lane + j * 32 < chunks) {
-        gemv_step<kRows, kLanesPerGroup>(p, current[j], base + j * 32, chunks, lane, dots, groups);
+        gemv_step<kRows, kLanesPerGroup>(p, w[j], base + j * 32, chunks, lane, dots, groups);
       }
+      // The register is free again: its next load goes out at once, so that eight loads stay
+      // in flight per lane throughout.
+      const int chunk = next_base + j * 32;
+      w[j] = more && chunk < chunks ? ldg_stream_16(next + (static_cast<long long>(chunk) << 4))
+                                    : make_uint4(0u, 0u, 0u, 0u);
     }
   }
   __syncthreads();
