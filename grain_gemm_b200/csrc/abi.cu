@@ -596,6 +596,16 @@ int gg_moe_route(const void* ids, int ids_are_i64, const void* mask, int tokens,
     gg::route_single_kernel<<<1, gg::kRouteChunk, smem, stream>>>(p);
     return static_cast<int>(cudaGetLastError());
   }
+  if (slots <= gg::kRouteMediumSlots && experts + 1 <= gg::kRouteMediumKeys) {
+    const size_t medium = (static_cast<size_t>(33) * (experts + 1) + 33) * sizeof(int);
+    if (medium > 48 * 1024) {
+      error = cudaFuncSetAttribute(gg::route_medium_kernel,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(medium));
+      if (error != cudaSuccess) return static_cast<int>(error);
+    }
+    gg::route_medium_kernel<<<1, 1024, medium, stream>>>(p);
+    return static_cast<int>(cudaGetLastError());
+  }
   if (workspace_bytes < gg_moe_route_workspace_bytes(tokens, top_k, experts) || !workspace) {
     return static_cast<int>(cudaErrorInvalidValue);
   }
@@ -673,9 +683,7 @@ int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, 
   if (!offsets || !tile_expert || !tile_row || experts <= 0 || tile_rows <= 0 || capacity <= 0) {
     return static_cast<int>(cudaErrorInvalidValue);
   }
-  const size_t smem = static_cast<size_t>(experts + 1) * sizeof(int);
-  if (smem > 48 * 1024) return static_cast<int>(cudaErrorInvalidValue);
-  gg::moe_tiles_kernel<<<1, 1024, smem, static_cast<cudaStream_t>(stream)>>>(
+  gg::moe_tiles_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const int*>(offsets), experts, tile_rows, capacity, static_cast<int*>(tile_expert),
       static_cast<int*>(tile_row));
   return static_cast<int>(cudaGetLastError());

@@ -115,6 +115,138 @@ __global__ void __launch_bounds__(kRouteChunk) route_single_kernel(const RoutePa
   route_single_body(p, bins);
 }
 
+// Routing problems of up to kRouteMediumSlots assignments and kRouteMediumKeys - 1 experts in
+// ONE CTA of 32 warps, instead of three launches with serial sections.  Every warp owns a
+// contiguous range of the assignments and walks it in rounds of 32:
+//   1. keys and a private per-warp histogram (lanes with equal keys elect a leader);
+//   2. per key an exclusive prefix over the warps, then a block-wide exclusive scan over the
+//      keys: base[warp][key] = first slot of that key for that warp;
+//   3. the same walk again: slot = base + rank among equal keys of the round, bases advance.
+// Warps are ordered, rounds are ordered and lanes are ordered, so the sort is stable, like the
+// chunked kernels (and the reference's argsort with stable=True).
+constexpr int kRouteMediumRounds = 8;
+constexpr int kRouteMediumSlots = 32 * 32 * kRouteMediumRounds;   // 8192 assignments
+constexpr int kRouteMediumKeys = 512;                              // experts + 1 at most
+
+__global__ void __launch_bounds__(1024) route_medium_kernel(const RouteParams p) {
+  extern __shared__ int medium_smem[];     // [32][keys] per-warp histograms / bases, then scratch
+  const int keys = p.experts + 1;
+  int* warp_bins = medium_smem;
+  int* key_total = medium_smem + 32 * keys;        // [keys] totals, then first slots
+  int* scan_scratch = key_total + keys;            // [32] warp totals of the block scan
+  int* invalid_total = scan_scratch + 32;          // [1]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long slots = static_cast<long long>(p.tokens) * p.top_k;
+  for (int i = threadIdx.x; i < 32 * keys; i += 1024) warp_bins[i] = 0;
+  if (threadIdx.x == 0) *invalid_total = 0;
+  __syncthreads();
+
+  const int per_warp = static_cast<int>((slots + 31) / 32 + 31) / 32 * 32;   // multiple of 32
+  const long long warp_begin = static_cast<long long>(warp) * per_warp;
+  int* bins = warp_bins + warp * keys;
+  int key[kRouteMediumRounds];
+  int invalid_count = 0;
+#pragma unroll
+  for (int r = 0; r < kRouteMediumRounds; ++r) {
+    const long long s = warp_begin + r * 32 + lane;
+    const bool present = r * 32 < per_warp && s < slots;
+    key[r] = -1;
+    if (present) {
+      bool invalid;
+      key[r] = route_key(p, s, invalid);
+      invalid_count += invalid ? 1 : 0;
+    }
+    const unsigned active = __ballot_sync(0xffffffffu, present);
+    if (present) {
+      const unsigned same = __match_any_sync(active, key[r]);
+      if (lane == __ffs(same) - 1) bins[key[r]] += __popc(same);
+    }
+    __syncwarp();
+  }
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    invalid_count += __shfl_xor_sync(0xffffffffu, invalid_count, offset);
+  }
+  if (lane == 0 && invalid_count) atomicAdd(invalid_total, invalid_count);
+  __syncthreads();
+
+  // Per key: exclusive prefix over the warps and the key's total.
+  for (int k = threadIdx.x; k < keys; k += 1024) {
+    int running = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int count = warp_bins[w * keys + k];
+      warp_bins[w * keys + k] = running;
+      running += count;
+    }
+    key_total[k] = running;
+  }
+  __syncthreads();
+  // Block-wide exclusive scan of key_total (keys <= 512: one value per thread of 16 warps).
+  int value = threadIdx.x < keys ? key_total[threadIdx.x] : 0;
+  int inclusive = value;
+  for (int offset = 1; offset < 32; offset <<= 1) {
+    const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+    if (lane >= offset) inclusive += other;
+  }
+  if (lane == 31) scan_scratch[warp] = inclusive;
+  __syncthreads();
+  if (warp == 0) {
+    const int total = scan_scratch[lane];
+    int scanned = total;
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const int other = __shfl_up_sync(0xffffffffu, scanned, offset);
+      if (lane >= offset) scanned += other;
+    }
+    scan_scratch[lane] = scanned - total;
+  }
+  __syncthreads();
+  const int first_slot = scan_scratch[warp] + inclusive - value;
+  if (threadIdx.x < keys) {
+    key_total[threadIdx.x] = first_slot;
+    if (threadIdx.x < p.experts) {
+      p.counts[threadIdx.x] = value;
+      p.offsets[threadIdx.x + 1] = first_slot + value;
+    }
+    if (threadIdx.x == 0) p.offsets[0] = 0;
+  }
+  // Largest expert count (statistics[1]).
+  int largest = threadIdx.x < p.experts ? value : 0;
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, offset));
+  }
+  __syncthreads();                       // scan_scratch is read above, rewritten below
+  if (lane == 0) scan_scratch[warp] = largest;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int maximum = 0;
+    for (int w = 0; w < 32; ++w) maximum = max(maximum, scan_scratch[w]);
+    p.statistics[0] = *invalid_total;
+    p.statistics[1] = maximum;
+    p.statistics[2] = key_total[p.experts];     // first slot of the ignored tail = valid total
+  }
+
+  // Placement: the same walk, against base[warp][key] = first slot of the key + warp prefix.
+#pragma unroll
+  for (int r = 0; r < kRouteMediumRounds; ++r) {
+    const long long s = warp_begin + r * 32 + lane;
+    const bool present = key[r] >= 0;
+    const unsigned active = __ballot_sync(0xffffffffu, present);
+    if (present) {
+      const unsigned same = __match_any_sync(active, key[r]);
+      const int leader = __ffs(same) - 1;
+      int first = 0;
+      if (lane == leader) {
+        first = key_total[key[r]] + bins[key[r]];
+        bins[key[r]] += __popc(same);
+      }
+      first = __shfl_sync(same, first, leader);
+      const int slot = first + __popc(same & ((1u << lane) - 1u));
+      p.order[slot] = s;
+      p.inverse[s] = key[r] < p.experts ? slot : -1;
+    }
+    __syncwarp();
+  }
+}
+
 __global__ void __launch_bounds__(kRouteChunk) route_histogram_kernel(const RouteParams p) {
   extern __shared__ int bins[];
   const long long slots = static_cast<long long>(p.tokens) * p.top_k;
@@ -192,28 +324,50 @@ report_to_host_kernel(const int* __restrict__ values, int count, int* host_words
 
 // Row-tile list for the grouped kernels: every expert's sorted rows are cut into tiles of
 // `tile_rows`; tile_expert/tile_row have room for ceil(S / tile_rows) + E entries, unused
-// entries get expert -1.  One CTA.
+// entries get expert -1.  One CTA: a block-wide exclusive scan of the experts' tile counts,
+// 1024 experts at a time.
 __global__ void __launch_bounds__(1024)
 moe_tiles_kernel(const int* __restrict__ offsets, int experts, int tile_rows, int max_tiles,
                  int* __restrict__ tile_expert, int* __restrict__ tile_row) {
-  extern __shared__ int first_tile[];  // [E + 1]
-  if (threadIdx.x == 0) {
-    int running = 0;
-    for (int e = 0; e < experts; ++e) {
-      first_tile[e] = running;
-      running += (offsets[e + 1] - offsets[e] + tile_rows - 1) / tile_rows;
-    }
-    first_tile[experts] = running;
-  }
+  __shared__ int warp_total[32];
+  __shared__ int carry;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) carry = 0;
   __syncthreads();
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-    const int begin = offsets[e];
-    for (int t = first_tile[e]; t < first_tile[e + 1]; ++t) {
-      tile_expert[t] = e;
-      tile_row[t] = begin + (t - first_tile[e]) * tile_rows;
+  for (int base = 0; base < experts; base += 1024) {
+    const int e = base + threadIdx.x;
+    int begin = 0, tiles = 0;
+    if (e < experts) {
+      begin = offsets[e];
+      tiles = (offsets[e + 1] - begin + tile_rows - 1) / tile_rows;
     }
+    int inclusive = tiles;
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+      if (lane >= offset) inclusive += other;
+    }
+    if (lane == 31) warp_total[warp] = inclusive;
+    __syncthreads();
+    if (warp == 0) {
+      const int total = warp_total[lane];
+      int scanned = total;
+      for (int offset = 1; offset < 32; offset <<= 1) {
+        const int other = __shfl_up_sync(0xffffffffu, scanned, offset);
+        if (lane >= offset) scanned += other;
+      }
+      warp_total[lane] = scanned - total;
+    }
+    __syncthreads();
+    const int first = carry + warp_total[warp] + inclusive - tiles;
+    for (int t = 0; t < tiles; ++t) {
+      tile_expert[first + t] = e;
+      tile_row[first + t] = begin + t * tile_rows;
+    }
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = first + tiles;
+    __syncthreads();
   }
-  for (int t = first_tile[experts] + threadIdx.x; t < max_tiles; t += blockDim.x) {
+  for (int t = carry + threadIdx.x; t < max_tiles; t += blockDim.x) {
     tile_expert[t] = -1;
     tile_row[t] = 0;
   }
