@@ -90,7 +90,8 @@ def test_routes_match_reference_fixtures(moe, name):
 @pytest.mark.parametrize("tokens,top_k,experts,dtype", [
     (0, 3, 5, torch.int64), (1, 1, 1, torch.int32), (128, 8, 128, torch.int32),
     (1024, 1, 7, torch.int64), (1025, 1, 7, torch.int64), (512, 8, 128, torch.int64),
-    (16384, 8, 256, torch.int32), (4096, 2, 8, torch.int64), (3000, 5, 1000, torch.int32)])
+    (16384, 8, 256, torch.int32), (4096, 2, 8, torch.int64), (3000, 5, 1000, torch.int32),
+    (8192, 1, 511, torch.int32), (1366, 6, 33, torch.int64), (2048, 4, 512, torch.int32)])
 def test_routes_match_oracle(moe, tokens, top_k, experts, dtype):
     gen = torch.Generator().manual_seed(tokens + experts)
     ids = torch.randint(-2, experts + 2, (tokens, top_k), generator=gen).to(dtype)
@@ -102,19 +103,21 @@ def test_routes_match_oracle(moe, tokens, top_k, experts, dtype):
         assert_routes_equal(routes, expected)
 
 
-def test_tile_list(moe):
+@pytest.mark.parametrize("count", [9, 2500])
+def test_tile_list(moe, count):
+    """The tile list is a scan over the experts, 1024 at a time: few and many experts."""
     gen = torch.Generator().manual_seed(4)
-    ids = torch.randint(0, 9, (700, 2), generator=gen)
+    ids = torch.randint(0, count, (700, 2), generator=gen)
     for tile_rows in (32, 128):
-        routes = moe.prepare_routes(ids.cuda(), 9, None, tile_rows=tile_rows)
+        routes = moe.prepare_routes(ids.cuda(), count, None, tile_rows=tile_rows)
         offsets = routes.offsets.cpu().tolist()
         experts, rows = [], []
-        for e in range(9):
+        for e in range(count):
             for start in range(offsets[e], offsets[e + 1], tile_rows):
                 experts.append(e)
                 rows.append(start)
         used = len(experts)
-        assert routes.tile_expert.numel() == (1400 + tile_rows - 1) // tile_rows + 9
+        assert routes.tile_expert.numel() == (1400 + tile_rows - 1) // tile_rows + count
         assert routes.tile_expert[:used].cpu().tolist() == experts
         assert routes.tile_row[:used].cpu().tolist() == rows
         assert (routes.tile_expert[used:] < 0).all()
