@@ -259,11 +259,12 @@ static GemmSimtParams simt_params(const GemmArgs& g) {
   return p;
 }
 
-template <int kCtaGroup, int BN, int kStages, typename OutT, bool kGrouped, int kPromoWarps>
+template <int kCtaGroup, int BN, int kStages, typename OutT, bool kGrouped, int kPromoWarps,
+          int kARows = 128>
 static int launch_tc_kernel(const CUtensorMap& map_a, const CUtensorMap& map_b,
                             const GemmTcParams& p, cudaStream_t stream) {
-  using Shape = GemmTcShape<kCtaGroup, BN, kStages, kPromoWarps>;
-  auto kernel = gemm_tc_kernel<kCtaGroup, BN, kStages, OutT, kGrouped, kPromoWarps>;
+  using Shape = GemmTcShape<kCtaGroup, BN, kStages, kPromoWarps, kARows>;
+  auto kernel = gemm_tc_kernel<kCtaGroup, BN, kStages, OutT, kGrouped, kPromoWarps, false, kARows>;
   cudaError_t error =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape::kSmemBytes);
   if (error != cudaSuccess) return static_cast<int>(error);
@@ -307,17 +308,17 @@ static int launch_tc_kernel(const CUtensorMap& map_a, const CUtensorMap& map_b,
   return static_cast<int>(error);
 }
 
-template <int kCtaGroup, int BN, int kStages, bool kGrouped, int kPromoWarps = 8>
+template <int kCtaGroup, int BN, int kStages, bool kGrouped, int kPromoWarps = 8, int kARows = 128>
 static int launch_tc_dtype(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmTcParams& p,
                            int out_dtype, cudaStream_t stream) {
   switch (out_dtype) {
     case GG_OUT_FP32:
       if constexpr (kGrouped) return static_cast<int>(cudaErrorInvalidValue);
-      else return launch_tc_kernel<kCtaGroup, BN, kStages, float, kGrouped, kPromoWarps>(map_a, map_b, p, stream);
+      else return launch_tc_kernel<kCtaGroup, BN, kStages, float, kGrouped, kPromoWarps, kARows>(map_a, map_b, p, stream);
     case GG_OUT_BF16:
-      return launch_tc_kernel<kCtaGroup, BN, kStages, __nv_bfloat16, kGrouped, kPromoWarps>(map_a, map_b, p, stream);
+      return launch_tc_kernel<kCtaGroup, BN, kStages, __nv_bfloat16, kGrouped, kPromoWarps, kARows>(map_a, map_b, p, stream);
     case GG_OUT_FP16:
-      return launch_tc_kernel<kCtaGroup, BN, kStages, __half, kGrouped, kPromoWarps>(map_a, map_b, p, stream);
+      return launch_tc_kernel<kCtaGroup, BN, kStages, __half, kGrouped, kPromoWarps, kARows>(map_a, map_b, p, stream);
     default: return static_cast<int>(cudaErrorInvalidValue);
   }
 }

@@ -579,6 +579,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       const int n0 = tn * BN;
       const bool row_ok = row < row_limit;
+      // Rows of this warp: 32 consecutive ones of the tile, the same for every lane.
+      const bool warp_has_rows = row - row_in_cta + quarter * 32 < row_limit;
       if constexpr (kDump) {
         // Split-K: hand the exact INT32 group dots to the folding kernel.
         for (int g = 0; g < groups; ++g, ++group_sequence) {
@@ -595,7 +597,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                              col_base;
           // Rows at or beyond M hold zero-filled operands; a warp whose 32 rows are all
           // beyond M skips the drain altogether.
-          const bool warp_has_rows = (row - lane) < row_limit;
           if (ok && warp_has_rows) {
 #pragma unroll
             for (int chunk = 0; chunk < kNC / 32; ++chunk) {
@@ -661,7 +662,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // of the next fragment is in flight while the current one is promoted.
         uint32_t partial_a[16], partial_b[16];
         float2 sb[4];
-        if (ok) {
+        if (ok && !warp_has_rows) {
+          // None of this warp's 32 rows exists (a skinny problem, the ragged end of an expert):
+          // nothing to promote, the buffer goes straight back.
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kCtaGroup == 1) mbar_arrive(&tmem_empty_bar[buffer]);
+            else mbar_arrive_cluster(&tmem_empty_bar[buffer], 0);
+          }
+        } else if (ok) {
           tmem_ld_fragment<kLayout>(taddr_low, partial_a);
 #pragma unroll
           for (int fragment = 0; fragment < 2 * kBlocks; ++fragment) {

@@ -236,6 +236,18 @@ def test_weight_streaming_kernel_for_a_handful_of_rows_is_bit_exact(gg, m, n, k,
         run(gg, linear_case(2, 64, 264, g, seed=1, scale="lognormal"), g, torch.float32, "gemv")
 
 
+@pytest.mark.parametrize("g", [32, 256])
+@pytest.mark.parametrize("m", [9, 33, 64, 65])
+def test_tiles_with_whole_warps_of_missing_rows_are_bit_exact(gg, m, g):
+    """Promotion warps whose 32 rows lie beyond M hand their accumulator buffer straight back;
+    the warps that have rows must not notice (9, 33, 64 and 65 rows: one to three such warps)."""
+    tensors = linear_case(m, 520, 1040, g, seed=m + g, scale="lognormal")
+    for dtype in (torch.float32, torch.bfloat16):
+        expected = oracle.int8_gemm(*tensors, g, dtype)
+        for variant in ("tc_n64", "tc_n256"):
+            assert torch.equal(run(gg, tensors, g, dtype, variant), expected), (m, g, dtype, variant)
+
+
 @pytest.mark.parametrize("m", [1, 16, 128])
 def test_skinny_m(gg, m):
     tensors = linear_case(m, 2048, 2048, 128, seed=m, scale="lognormal")
