@@ -49,7 +49,9 @@ NCU_TRAFFIC_BYTES = {"gemm_g256_m8192_n8192_k8192_bf16": 250927360 + 119968000}
 def parse():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
+    # 50 steps: the burst regime of the kernel timed alone (`roofline.peak` is the burst figure
+    # too); the seconds-long rate under the power cap is reported beside it under `sustained`.
+    parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--moe-config", default="large",
