@@ -847,6 +847,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
+    if constexpr (kGrouped) {
+      // Rows stored into another GPU's memory are consumed there after a collective that
+      // follows this kernel in the stream.
+      if (p.row_destination != nullptr) __threadfence_system();
+    }
   }
 
   tcgen05_fence_before();
