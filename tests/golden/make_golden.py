@@ -13,7 +13,14 @@ Two sources are used, both the reference's own code, unmodified:
   tensors by Triton's interpreter (``TRITON_INTERPRET=1``).  The interpreter's
   ``fma`` is an unfused multiply-add, so it is replaced here by an exact
   ``fmaf`` to keep the kernels' documented fused semantics; integer kernels
-  (routing) need no patch.
+  (routing) need no patch.  The SwiGLU/requantisation and combine kernels call libdevice
+  (``div_rn``, ``nearbyint``, ``exp``), which the interpreter cannot run: IEEE stand-ins on
+  float32 arrays replace them (``libdevice_stand_ins``), and the fixture carries silu of every
+  BF16 value as computed with them, so that a test can take the exponential out of the
+  comparison.
+
+``python tests/golden/make_golden.py stages`` (or ``gemm``, ``routing``, ``moe``) regenerates one
+family.
 
 The fixtures are small ``.npz`` files; the tests never need the reference.
 """
@@ -28,7 +35,9 @@ if "GRAIN_REFERENCE_DIR" not in os.environ:
 REFERENCE = Path(os.environ["GRAIN_REFERENCE_DIR"])
 sys.path.insert(0, str(REFERENCE / "src"))
 sys.path.insert(0, str(REFERENCE / "tests"))
-sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+# Behind the reference on the path: this repository's optional `grain_gemm` drop-in package must
+# not shadow the reference's package of the same name.
+sys.path.append(str(Path(__file__).resolve().parents[2]))
 
 import numpy as np
 import torch
@@ -161,7 +170,69 @@ def moe_fixtures():
     save("quantizer_known", x=x, q=q, s=s)
 
 
+def libdevice_stand_ins():
+    """The stage kernels call libdevice (``div_rn``, ``exp``, ``nearbyint``), which the interpreter
+    cannot run.  Stand-ins with the same IEEE meaning on float32 numpy arrays: a correctly
+    rounded division, round-half-even, and the interpreter's own ``tl.exp``."""
+    import triton.language as tl
+
+    def elementwise(function):
+        def call(*operands, _semantic=None, **unused):
+            arrays = [o.handle.data if isinstance(o, tl.tensor) else np.float32(o) for o in operands]
+            first = next(o for o in operands if isinstance(o, tl.tensor))
+            result = np.asarray(function(*arrays), dtype=np.float32)
+            return tl.tensor(interpreter.TensorHandle(result, tl.float32), first.type)
+        return call
+
+    ref_moe_kernels.libdevice.div_rn = elementwise(
+        lambda a, b: np.divide(np.asarray(a, np.float32), np.asarray(b, np.float32)))
+    ref_moe_kernels.libdevice.nearbyint = elementwise(np.rint)
+    ref_moe_kernels.libdevice.exp = elementwise(
+        lambda x: np.exp(np.asarray(x, np.float32)))
+
+
+def interpreter_silu_table():
+    """silu of every BF16 value with the operations the stand-ins use (numpy's float32 ``exp``,
+    not libdevice's): entry b = g / (1 + exp(-g)) for the value with bit
+    pattern b.  Handing this table to the oracle removes the one library call the two sides
+    cannot share and leaves everything else of the stage to be compared bit for bit."""
+    bits = np.arange(65536, dtype=np.uint32) << 16
+    gate = bits.view(np.float32)
+    with np.errstate(over="ignore", invalid="ignore"):
+        return (gate / (np.float32(1) + np.exp(-gate))).astype(np.float32)
+
+
+def stage_fixtures():
+    """The reference's ``swiglu_quantize`` and ``combine`` Triton kernels (kernels/moe.py:564-601,
+    634-653) under the interpreter, on inputs of their own (BF16 gate/up rows, BF16 expert
+    outputs), both layouts, ragged routes with an empty expert and masked tokens."""
+    libdevice_stand_ins()
+    generator = torch.Generator().manual_seed(11)
+    tokens, top_k, experts, inter, hidden = 37, 3, 6, 512, 256
+    ids = torch.randint(0, experts - 1, (tokens, top_k), generator=generator)   # expert 5 empty
+    mask = torch.rand((tokens,), generator=generator) > 0.2
+    routes = ref_moe_kernels.prepare_routes(ids, experts, mask, include_tiles=False)
+    slots = tokens * top_k
+    gate_up = (3.0 * torch.randn((slots, 2 * inter), generator=generator)).to(torch.bfloat16)
+    gate_up[0, :8] = torch.tensor([0.0, -0.0, 1.0, -1.0, 20.0, -20.0, 88.0, -88.0]).to(torch.bfloat16)
+    gate_up[1, :inter] = 0                         # a row whose activations are all zero
+    table = interpreter_silu_table()
+    arrays = dict(ids=ids, mask=mask, experts=experts, gate_up=gate_up, silu_table=table,
+                  offsets=routes.offsets, inverse=routes.inverse)
+    for layout in ("split", "interleaved"):
+        q, scales = ref_moe_kernels.swiglu_quantize(gate_up, routes=routes, gate_up_layout=layout)
+        arrays[f"q_{layout}"] = q
+        arrays[f"scale_{layout}"] = scales
+    expert_out = torch.randn((slots, hidden), generator=generator).to(torch.bfloat16)
+    weights = torch.rand((tokens, top_k), generator=generator)
+    # FP32 output: the interpreter truncates FP32 -> BF16 instead of rounding to nearest even.
+    combined = ref_moe_kernels.combine(expert_out, weights, routes, output_dtype=torch.float32)
+    save("moe_stages", expert_out=expert_out, topk_weights=weights, combined_fp32=combined, **arrays)
+
+
 if __name__ == "__main__":
-    gemm_fixtures()
-    routing_fixtures()
-    moe_fixtures()
+    only = sys.argv[1:]
+    for name, make in (("gemm", gemm_fixtures), ("routing", routing_fixtures), ("moe", moe_fixtures),
+                       ("stages", stage_fixtures)):
+        if not only or name in only:
+            make()
