@@ -10,7 +10,8 @@ box, both in the tests and the benchmark's context figures only, never in the pr
 * the "what a user of the reference gets on this GPU today" timing next to ours.
 
 Nothing is copied into the repository's history: the install goes through pip from the
-read-only reference tree (``GRAIN_REFERENCE``, default ``/root/reference``) via a temporary copy,
+read-only reference tree (``GRAIN_REFERENCE``, default: a ``reference`` folder beside this
+repository) via a temporary copy,
 ``--no-deps``, and lands in ``oracle/_ref`` only.  Only its Triton kernels are ever called; the
 reference's native (CuTe/CUTLASS) sources are removed from the install and never built.
 
@@ -31,7 +32,7 @@ TARGET = HERE / "_ref"
 
 
 def reference_root() -> Path:
-    return Path(os.environ.get("GRAIN_REFERENCE", "/root/reference"))
+    return Path(os.environ.get("GRAIN_REFERENCE", str(HERE.parents[1] / "reference")))
 
 
 def is_installed() -> bool:
