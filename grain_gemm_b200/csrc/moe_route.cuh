@@ -663,13 +663,13 @@ combine_kernel(const T* __restrict__ expert_out, const float* __restrict__ weigh
   if (vector_ok) {
     for (int col = threadIdx.x * 8; col < hidden; col += blockDim.x * 8) {
       float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      // Four rows are fetched before any is added, so that a thread keeps four 16-byte loads
+      // Eight rows are fetched before any is added, so that a thread keeps eight 16-byte loads
       // in flight; the additions stay in slot order.
-      for (int r0 = 0; r0 < top_k; r0 += 4) {
-        uint4 packed[4];
-        int slot[4];
+      for (int r0 = 0; r0 < top_k; r0 += 8) {
+        uint4 packed[8];
+        int slot[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 8; ++j) {
           slot[j] = r0 + j < top_k ? slot_smem[r0 + j] : -1;
           if (slot[j] >= 0) {
             packed[j] = *reinterpret_cast<const uint4*>(
@@ -677,7 +677,7 @@ combine_kernel(const T* __restrict__ expert_out, const float* __restrict__ weigh
           }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 8; ++j) {
           if (slot[j] < 0) continue;
           const float w = weight_smem[r0 + j];
           const T* values = reinterpret_cast<const T*>(&packed[j]);
