@@ -88,8 +88,9 @@ struct GemmArgs {
 
 static bool valid_group(int g) { return g == 32 || g == 64 || g == 128 || g == 256; }
 
-// Largest M the automatic choice gives to the weight-streaming kernel.
-constexpr int GEMV_AUTO_ROWS = 2;
+// The automatic choice gives one row to the weight-streaming kernel whatever the weights' size,
+// two rows up to this many weight bytes (measured: beyond it split-K is faster for two rows).
+constexpr long long kGemvTwoRowBytes = 32ll << 20;
 
 static bool tensor_core_layout(const GemmArgs& g) {
   return g.a_sk == 1 && g.b_sk == 1 && g.a_sm % 16 == 0 && g.b_sn % 16 == 0 && g.a_sm >= g.k &&
@@ -213,7 +214,9 @@ static int launch_gemv(const GemmArgs& g, cudaStream_t stream) {
 
 static int select_variant(const GemmArgs& g) {
   if (!tensor_core_layout(g)) return GG_VARIANT_SIMT;
-  if (g.m <= GEMV_AUTO_ROWS && gemv_eligible(g)) return GG_VARIANT_GEMV;
+  const bool gemv_rows_ok =
+      g.m == 1 || (g.m == 2 && static_cast<long long>(g.n) * g.k <= kGemvTwoRowBytes);
+  if (gemv_rows_ok && gemv_eligible(g)) return GG_VARIANT_GEMV;
   const int sms = sm_count();
   const long long tiles_256 = static_cast<long long>((g.m + 127) / 128) * ((g.n + 255) / 256);
   if (splitk_plan(g.m, g.n, g.k, g.group_size).splits >= 2) return GG_VARIANT_TC_SPLITK;
