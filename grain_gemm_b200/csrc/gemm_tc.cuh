@@ -719,6 +719,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quad = lane & 3;
         const int first_row = row - row_in_cta + quarter * 32 + fragment_row;
         const bool aligned = p.c_vector_ok != 0;
+        // Destination addresses of this thread's four rows and of the four rows of the lane it
+        // exchanges with, fetched in one batch before the first store: a load issued between
+        // the stores would wait behind them (the compiler must assume they alias), one round
+        // trip per row instead of one per tile.
+        [[maybe_unused]] unsigned long long own_destination[4] = {0ull, 0ull, 0ull, 0ull};
+        [[maybe_unused]] unsigned long long other_destination[4] = {0ull, 0ull, 0ull, 0ull};
+        if constexpr (kGrouped) {
+          if (p.row_destination != nullptr) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              const int out_row = first_row + 8 * r;
+              const int partner_row = out_row + (fragment_row < 4 ? 4 : -4);
+              if (out_row < row_limit) own_destination[r] = __ldg(p.row_destination + out_row);
+              if (partner_row < row_limit) other_destination[r] = __ldg(p.row_destination + partner_row);
+            }
+          }
+        }
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           const int out_row = first_row + 8 * r;
@@ -727,9 +744,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if constexpr (kGrouped) {
             if (p.row_destination != nullptr) {
               // The table holds the address of the row's first element; 0 = do not store.
-              const unsigned long long destination = row_stored ? p.row_destination[out_row] : 0ull;
-              row_stored = destination != 0ull;
-              c_row = reinterpret_cast<OutT*>(destination);
+              row_stored = own_destination[r] != 0ull;
+              c_row = reinterpret_cast<OutT*>(own_destination[r]);
             }
           }
           if constexpr (kGrouped && sizeof(OutT) == 2 && kBlocks % 2 == 0) {
@@ -739,9 +755,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // lines better than halves.  All conditions are the same in every lane.
             if (p.row_destination != nullptr && aligned && n0 + col_base + kNC <= p.n) {
               const bool low = fragment_row < 4;
-              const int partner_row = out_row + (low ? 4 : -4);
-              const unsigned long long partner_destination =
-                  partner_row < row_limit ? p.row_destination[partner_row] : 0ull;
+              const unsigned long long partner_destination = other_destination[r];
 #pragma unroll
               for (int block = 0; block < kBlocks; block += 2) {
                 uint32_t w[2][4];
