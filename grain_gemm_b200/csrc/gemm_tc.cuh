@@ -134,15 +134,15 @@ __device__ __forceinline__ void tile_coordinates(int tile, int tiles_m, int tile
   tn = local / band_m;
 }
 
-__device__ __forceinline__ TileWork decode_tile(const GemmTcParams& p, int tile) {
+__device__ __forceinline__ TileWork decode_tile(const GemmTcParams& p, int tile, int tiles_m) {
   TileWork w;
   int split = 0;
   if (p.k_splits > 1) {
-    const int per_split = p.tiles_m * p.tiles_n;
+    const int per_split = tiles_m * p.tiles_n;
     split = tile / per_split;
     tile -= split * per_split;
   }
-  tile_coordinates(tile, p.tiles_m, p.tiles_n, w.tm, w.tn, p.band_rows);
+  tile_coordinates(tile, tiles_m, p.tiles_n, w.tm, w.tn, p.band_rows);
   const int total_groups = (p.k + p.group_size - 1) / p.group_size;
   w.group_begin = split * p.groups_per_split;
   const int group_end = p.k_splits > 1 ? min(total_groups, w.group_begin + p.groups_per_split)
@@ -290,7 +290,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
   const int worker = blockIdx.x / kCtaGroup;
   const int workers = gridDim.x / kCtaGroup;
-  const int total_tiles = p.tiles_m * p.tiles_n * p.k_splits;
+  // (total_tiles follows the set-up below: the grouped kernel first finds how many row tiles
+  // of its list are in use.)
   const int steps_per_group = p.group_size / 32;
 
   if (threadIdx.x == 0) {
@@ -313,6 +314,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
   }
+  // Grouped problems: the row-tile list has room for the worst case and its used entries come
+  // first; the kernel walks only those.  (An expert-parallel rank's list is sized for every
+  // row it could receive, several times what it does receive.)
+  __shared__ int used_row_tiles;
+  if constexpr (kGrouped) {
+    if (threadIdx.x == 32) {
+      int low = 0, high = p.tiles_m;
+      while (low < high) {
+        const int middle = (low + high) >> 1;
+        if (p.tile_expert[middle] >= 0) low = middle + 1;
+        else high = middle;
+      }
+      used_row_tiles = low;
+    }
+  }
   if constexpr (kCtaGroup == 2) cluster_sync_all();
   if (warp == kMmaWarp) tmem_alloc<kCtaGroup>(tmem_holder, Shape::kTmemColumns);
   tcgen05_fence_before();
@@ -320,6 +336,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if constexpr (kCtaGroup == 2) cluster_sync_all();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  int tiles_m = p.tiles_m;
+  if constexpr (kGrouped) tiles_m = used_row_tiles;
+  const int total_tiles = tiles_m * p.tiles_n * p.k_splits;
   // The last four warps (producer, MMA issuer, two spares) give registers to the promotion warps.
   if (warp >= kPromoWarps) {
   setmaxnreg_dec<Shape::kAuxRegisters>();
@@ -330,7 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t stage = 0, phase = 0;
     bool ok = true;
     for (int tile = worker; tile < total_tiles && ok; tile += workers) {
-      const TileWork work = decode_tile(p, tile);
+      const TileWork work = decode_tile(p, tile, tiles_m);
       const int tm = work.tm, tn = work.tn;
       int row_a, row_b;
       if constexpr (kGrouped) {
@@ -381,7 +400,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int step = 0;                                  // MMAs issued into the open group
       bool ok = true;
       for (int tile = worker; tile < total_tiles && ok; tile += workers) {
-        const TileWork work = decode_tile(p, tile);
+        const TileWork work = decode_tile(p, tile, tiles_m);
         if constexpr (kGrouped) {
           if (p.tile_expert[work.tm] < 0) continue;
         }
@@ -488,7 +507,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t slot = 0, phase = 0;
     bool ok = true;
     for (int tile = worker; tile < total_tiles && ok; tile += workers) {
-      const TileWork work = decode_tile(p, tile);
+      const TileWork work = decode_tile(p, tile, tiles_m);
       int row0, row_limit;
       const float* sb_base = p.scale_b;
       if constexpr (kGrouped) {
@@ -562,7 +581,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // A failed wait clears `ok` but the loops keep their shape, so that every thread still
     // reaches every named barrier the others wait on.
     for (int tile = worker; tile < total_tiles; tile += workers) {
-      const TileWork work = decode_tile(p, tile);
+      const TileWork work = decode_tile(p, tile, tiles_m);
       const int tm = work.tm, tn = work.tn;
       const int groups = work.groups;
       int row, row_limit;

@@ -129,7 +129,6 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int channel_groups = p.intermediate / 256;
-  const int total_items = p.max_tiles * channel_groups;
   const int groups = p.hidden / 256;
   const int slabs = p.hidden / 128;
 
@@ -153,11 +152,25 @@ moe_gate_up_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     prefetch_tensormap(&map_x);
     prefetch_tensormap(&map_w);
   }
+  // The row-tile list has room for the worst case and its used entries come first; the kernel
+  // walks only those.  (An expert-parallel rank's list is sized for every row it could
+  // receive, several times what it does receive.)
+  __shared__ int used_row_tiles;
+  if (threadIdx.x == 32) {
+    int low = 0, high = p.max_tiles;
+    while (low < high) {
+      const int middle = (low + high) >> 1;
+      if (p.tile_expert[middle] >= 0) low = middle + 1;
+      else high = middle;
+    }
+    used_row_tiles = low;
+  }
   if (warp == 9) tmem_alloc<1>(tmem_holder, 512);
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  const int total_items = used_row_tiles * channel_groups;
   constexpr FragmentLayout kLayout = kFragmentPairs;
 
   // Warps 8-11 (producer, MMA issuer, two spares) give registers to the promotion warps.
