@@ -151,3 +151,25 @@ def test_moe_argument_errors_without_a_device():
         moe_ffn(**bad)
     with pytest.raises(ValueError, match="CUDA"):
         moe_ffn(**case)
+
+
+def test_measured_variant_table_is_well_formed():
+    """The shipped shape -> variant table: known variant names, ascending M bounds that end
+    open, one entry per (G, N, K) key, and the weight-streaming kernel only where it can run."""
+    import json
+    from pathlib import Path
+    table = json.loads((Path(grain_gemm_b200.__file__).parent / "configs"
+                        / "b200_sm100_variants.json").read_text())
+    assert table["shapes"]
+    for key, rows in table["shapes"].items():
+        group, n, k = (int(part) for part in key.split(":"))
+        assert group in (32, 64, 128, 256) and n > 0 and k > 0
+        bounds = [bound for bound, _ in rows]
+        assert bounds == sorted(bounds) and len(set(bounds)) == len(bounds)
+        assert bounds[-1] == 2 ** 31 - 1
+        for bound, name in rows:
+            assert name in _loader.VARIANTS and name != "auto", (key, name)
+            if name == "gemv":
+                assert bound <= 8 and k % 16 == 0, (key, bound)
+            if name == "tc_splitk":
+                assert bound <= 32, (key, bound)
