@@ -149,7 +149,9 @@ size_t gg_moe_route_noalloc_capacity_bytes(void);
 /* Entries tile_expert / tile_row must hold for S assignments, E experts, tiles of tile_rows. */
 int gg_moe_tile_capacity(int assignments, int experts, int tile_rows);
 
-/* Cuts every expert's sorted rows into tiles of tile_rows rows; unused entries get expert -1.
+/* Cuts every expert's sorted rows into tiles of tile_rows rows; the used entries come first,
+ * unused entries get expert -1 (gg_moe_gate_up and gg_moe_down rely on that order: they walk
+ * the list up to its first unused entry).
  * Replaces prepare_ragged_tiles (src/grain_gemm/kernels/moe.py:294-318). */
 int gg_moe_tiles(const void* offsets, int experts, int tile_rows, int capacity, void* tile_expert,
                  void* tile_row, void* stream);
